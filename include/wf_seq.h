@@ -1,0 +1,89 @@
+/* C ABI of libwf_seq.so: the serving engine for sequence models built as a stack of heterogeneous layers (an attention or a recurrent
+ * mixer, then an optional routed feed-forward) — paged caches, fixed-size per-sequence state slots, ragged steps that mix prompt portions
+ * with single decoded tokens.  Same conventions as wf_bitnet.h: plain pointers and sizes, int status (0 ok, -1 invalid argument,
+ * -2 unsupported, -3 CUDA error), wf_last_error() has the text; nothing throws, nothing prints. */
+#ifndef WF_SEQ_H
+#define WF_SEQ_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WF_SEQ_F32 0
+#define WF_SEQ_BF16 1
+
+#define WF_SEQ_LATENT_ATTENTION 0  /* sliding-window attention over a cached low-rank latent + one shared rotated key part */
+#define WF_SEQ_DELTA 1             /* gated delta rule with short convolutions */
+
+typedef struct wf_seq_layer {
+    int type;
+    int heads, dim, vdim;          /* both mixers: heads, query/key size per head (unrotated part for latent attention), value size */
+    /* latent attention */
+    int rot_dim, kv_rank, window, rope_dims;
+    float scale, rope_base;
+    /* delta */
+    int kv_heads, conv;
+    /* routed feed-forward (has_ff = 0: the layer has none) */
+    int has_ff, experts, identity, top, groups, keep, ff;
+} wf_seq_layer;
+
+typedef struct wf_seq_config {
+    int dtype;                     /* WF_SEQ_BF16: bf16 weights, caches and matrix-product operands; WF_SEQ_F32: everything in float */
+    int vocab, width, n_layers;
+    float eps;
+    int norm_groups, canon_taps;
+    int page_size, max_pages;      /* cache pool: max_pages pages of page_size tokens (all cached layers of a token share a page) */
+    int slots;                     /* sequences alive at once (each owns one state slot and one block-table row) */
+    int max_step_tokens;           /* most tokens in one step */
+} wf_seq_config;
+
+typedef struct wf_seq_engine wf_seq_engine;
+
+int wf_seq_available(void);
+int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layers, wf_seq_engine** out);
+void wf_seq_destroy(wf_seq_engine* e);
+size_t wf_seq_device_bytes(const wf_seq_engine* e);
+/* Upload one checkpoint tensor by its checkpoint name ('embed', 'l3.mix.q', 'l0.mlp.e7.down', ...); data holds `count` elements of the
+ * engine's dtype (host or device memory).  The engine lays the pieces out for its kernels (fused projections, stacked experts). */
+int wf_seq_set_tensor(wf_seq_engine* e, const char* name, const void* data, size_t count, int is_host);
+/* number of tensors the engine expects; name of the i-th and its element count (loader support, also lists what is still missing) */
+int wf_seq_tensor_count(const wf_seq_engine* e);
+const char* wf_seq_tensor_name(const wf_seq_engine* e, int i, size_t* count, int* loaded);
+int wf_seq_finalize(wf_seq_engine* e);
+
+/* Sequence life cycle.  admit: a free slot with zeroed state, length 0 (-1 in *slot when none is free: not an error).
+ * release: its pages and its slot go back to the free lists. */
+int wf_seq_admit(wf_seq_engine* e, int* slot);
+int wf_seq_release(wf_seq_engine* e, int slot);
+int wf_seq_length(const wf_seq_engine* e, int slot);
+int wf_seq_free_pages(const wf_seq_engine* e);
+int wf_seq_free_slots(const wf_seq_engine* e);
+
+/* One step: sequence i (slot slots[i]) advances by counts[i] tokens taken in order from `tokens`; all of them run as one ragged batch.
+ * want[j] are indices into the flat token list whose logits are computed (float [nwant, vocab], kept on the device until the next
+ * step; copied to logits_host when that is not null).  Synchronous. */
+int wf_seq_step(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t* counts, const int32_t* tokens, int nwant,
+                const int32_t* want, float* logits_host);
+/* Draw one token per wanted row of the last step: temperature <= 0 is greedy; else softmax(logits / temperature) limited to the top_k
+ * most likely (0: all) and to the smallest set whose mass reaches top_p (>= 1: all); uniforms: one number in [0, 1) per row. */
+int wf_seq_sample(wf_seq_engine* e, int nwant, float temperature, int top_k, float top_p, const float* uniforms_host, int32_t* next_host);
+void* wf_seq_logits_device(wf_seq_engine* e);
+int wf_seq_launches_last_step(const wf_seq_engine* e);
+
+/* Parity taps.  layer_tap: when not null, the residual stream after every layer of the next steps is copied there
+ * (float [n_layers, n, width], n = tokens of the step).  wf_seq_run_part runs ONE part of one layer on given float rows (host memory,
+ * [n, width]) through the same kernels, caches and state as wf_seq_step, and returns that part's float output [n, width]:
+ * 0 first norm, 1 input convolution of the mixer (carried state), 2 the mixer, 3 the feed-forward, 4 input convolution of the
+ * feed-forward.  Sequence lengths advance as in a step. */
+int wf_seq_set_layer_tap(wf_seq_engine* e, float* host);
+int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, const int32_t* slots, const int32_t* counts, const float* in_host,
+                    float* out_host);
+/* mean device time of the kernels of one step shape, by kind (measurement): runs the step `iters` times on synthetic tokens and returns
+ * milliseconds per step */
+int wf_seq_time_step(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t* counts, int iters, float* ms_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WF_SEQ_H */

@@ -7,39 +7,6 @@
 
 namespace wf {
 
-static thread_local char g_err[512] = "";
-
-void set_error(const char* fmt, ...) {
-    va_list ap;
-    va_start(ap, fmt);
-    vsnprintf(g_err, sizeof g_err, fmt, ap);
-    va_end(ap);
-}
-
-int cuda_check(cudaError_t e, const char* what) {
-    if (e == cudaSuccess) return WF_OK;
-    set_error("%s: CUDA error %d (%s)", what, (int)e, cudaGetErrorString(e));
-    return WF_ERR_CUDA;
-}
-
-static thread_local long long g_launches = 0;
-int launch_check(cudaError_t e, const char* what) {
-    ++g_launches;
-    return cuda_check(e, what);
-}
-long long launch_count() { return g_launches; }
-
-int sm_count() {
-    static int per_dev[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev > 63) dev = 0;
-    int& n = per_dev[dev];
-    if (n == 0) {
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
-    return n;
-}
-
 int fill_epi(const wf_linear_args* a, EpiParams* p) {
     memset(p, 0, sizeof *p);
     p->M = a->M;
@@ -87,7 +54,6 @@ int fill_epi(const wf_linear_args* a, EpiParams* p) {
 
 using namespace wf;
 
-extern "C" const char* wf_last_error(void) { return g_err; }
 extern "C" const char* wf_version(void) { return "wf_bitnet b200 r1"; }
 extern "C" int wf_sm_count(void) { return sm_count(); }
 extern "C" int wf_copy_d2d(void* dst, const void* src, size_t bytes, void* stream) {

@@ -1,0 +1,162 @@
+// Gated delta rule: a per-head matrix state S [d, dv] in float that every token first decays, then corrects along its key
+// (u = beta (v - S^T k), S += k u^T) and finally reads with its query (o = S^T q).  The state is carried per sequence slot across steps.
+#include "seq_kernels.cuh"
+
+namespace wf {
+namespace seq {
+
+namespace {
+
+// one block per token: unit-normalise the q and k heads in place, compute the write strength and the decay of every head
+template <typename T>
+__global__ void delta_prep_kernel(DeltaDims D, float* __restrict__ qkv, int ld, const float* __restrict__ a_raw, int lda, const float* __restrict__ b_raw,
+                                  int ldb, const T* __restrict__ A_log, const T* __restrict__ dt_bias, float* __restrict__ beta, float* __restrict__ decay) {
+    const int i = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float* row = qkv + (size_t)i * ld;
+    const float qscale = 1.f / sqrtf((float)D.d);
+    for (int v = warp; v < 2 * D.Hk; v += nw) {          // vectors 0 .. Hk-1 are q heads, Hk .. 2Hk-1 are k heads
+        float* x = row + (size_t)v * D.d;
+        float ss = 0.f;
+        for (int c = lane; c < D.d; c += 32) ss += x[c] * x[c];
+        ss = warp_sum(ss);
+        const float inv = (v < D.Hk ? qscale : 1.f) / sqrtf(ss + 1e-6f);
+        for (int c = lane; c < D.d; c += 32) x[c] *= inv;
+    }
+    for (int h = threadIdx.x; h < D.H; h += blockDim.x) {
+        beta[(size_t)i * D.H + h] = sigmoid_f(b_raw[(size_t)i * ldb + h]);
+        const float sp = softplus_f(a_raw[(size_t)i * lda + h] + to_f(dt_bias[h]));
+        decay[(size_t)i * D.H + h] = expf(-expf(to_f(A_log[h])) * sp);
+    }
+}
+
+constexpr int DR_COLS = 32, DR_PARTS = 4, DR_TT = 8;
+
+// block = (sequence, head, 32 value columns); thread = (column, quarter of the key rows), its part of the column in registers
+template <int DPT>
+__global__ void __launch_bounds__(DR_COLS * DR_PARTS) delta_rule_kernel(Batch b, DeltaDims D, const float* __restrict__ qkv, int ld,
+                                                                         const float* __restrict__ beta, const float* __restrict__ decay,
+                                                                         float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
+    extern __shared__ float sm[];
+    float* ks = sm;                         // [TT][d]
+    float* qs = ks + DR_TT * D.d;           // [TT][d]
+    float* vs = qs + DR_TT * D.d;           // [TT][32]
+    float* bs = vs + DR_TT * DR_COLS;       // [TT]
+    float* gs = bs + DR_TT;                 // [TT]
+    const int sq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
+    const int tid = threadIdx.x, p = tid % DR_PARTS, jl = tid / DR_PARTS, col = col0 + jl;
+    const bool col_ok = col < D.dv;
+    const int kh = h / (D.H / D.Hk);
+    const int start = b.seq_start[sq], len = b.seq_len[sq];
+    float* S = state + (size_t)b.seq_slot[sq] * slot_stride + (size_t)h * D.d * D.dv;
+    float s[DPT];
+#pragma unroll
+    for (int m = 0; m < DPT; ++m) {
+        const int i = p + DR_PARTS * m;
+        s[m] = (col_ok && i < D.d) ? S[(size_t)i * D.dv + col] : 0.f;
+    }
+    const int q_off = kh * D.d, k_off = (D.Hk + kh) * D.d, v_off = 2 * D.Hk * D.d + h * D.dv;
+    for (int t0 = 0; t0 < len; t0 += DR_TT) {
+        const int tt = len - t0 < DR_TT ? len - t0 : DR_TT;
+        __syncthreads();
+        for (int idx = tid; idx < tt * D.d; idx += blockDim.x) {
+            const int t = idx / D.d, c = idx % D.d;
+            const float* row = qkv + (size_t)(start + t0 + t) * ld;
+            ks[t * D.d + c] = row[k_off + c];
+            qs[t * D.d + c] = row[q_off + c];
+        }
+        for (int idx = tid; idx < tt * DR_COLS; idx += blockDim.x) {
+            const int t = idx / DR_COLS, c = idx % DR_COLS;
+            vs[idx] = col0 + c < D.dv ? qkv[(size_t)(start + t0 + t) * ld + v_off + col0 + c] : 0.f;
+        }
+        if (tid < tt) {
+            bs[tid] = beta[(size_t)(start + t0 + tid) * D.H + h];
+            gs[tid] = decay[(size_t)(start + t0 + tid) * D.H + h];
+        }
+        __syncthreads();
+        for (int t = 0; t < tt; ++t) {
+            const float* kt = ks + t * D.d;
+            const float* qt = qs + t * D.d;
+            const float g = gs[t];
+            float r = 0.f;
+#pragma unroll
+            for (int m = 0; m < DPT; ++m) {
+                const int i = p + DR_PARTS * m;
+                if (i < D.d) r = fmaf(s[m], kt[i], r);
+            }
+            r += __shfl_xor_sync(0xffffffffu, r, 1);
+            r += __shfl_xor_sync(0xffffffffu, r, 2);
+            const float u = bs[t] * (vs[t * DR_COLS + jl] - g * r);
+            float out = 0.f;
+#pragma unroll
+            for (int m = 0; m < DPT; ++m) {
+                const int i = p + DR_PARTS * m;
+                if (i < D.d) {
+                    s[m] = fmaf(kt[i], u, g * s[m]);
+                    out = fmaf(s[m], qt[i], out);
+                }
+            }
+            out += __shfl_xor_sync(0xffffffffu, out, 1);
+            out += __shfl_xor_sync(0xffffffffu, out, 2);
+            if (p == 0 && col_ok) o[((size_t)(start + t0 + t) * D.H + h) * D.dv + col] = out;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < DPT; ++m) {
+        const int i = p + DR_PARTS * m;
+        if (col_ok && i < D.d) S[(size_t)i * D.dv + col] = s[m];
+    }
+}
+
+template <typename T>
+__global__ void delta_post_kernel(DeltaDims D, const float* __restrict__ o, const T* __restrict__ w, float eps, const float* __restrict__ g, int ldg,
+                                  T* __restrict__ y) {
+    const int i = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int h = warp; h < D.H; h += nw) {
+        const float* x = o + ((size_t)i * D.H + h) * D.dv;
+        float ss = 0.f;
+        for (int c = lane; c < D.dv; c += 32) ss += x[c] * x[c];
+        ss = warp_sum(ss);
+        const float inv = 1.f / sqrtf(ss / (float)D.dv + eps);
+        for (int c = lane; c < D.dv; c += 32)
+            y[((size_t)i * D.H + h) * D.dv + c] = from_f<T>(x[c] * inv * to_f(w[c]) * silu_f(g[(size_t)i * ldg + (size_t)h * D.dv + c]));
+    }
+}
+
+}  // namespace
+
+int launch_delta_prep(int dt, const DeltaDims& D, int n, float* qkv, int ld, const float* a_raw, int lda, const float* b_raw, int ldb_,
+                      const void* A_log, const void* dt_bias, float* beta, float* decay, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (D.Hk <= 0 || D.H % D.Hk) { set_error("delta: %d heads over %d key heads", D.H, D.Hk); return WF_ERR_INVALID; }
+    if (dt == WF_BF16) delta_prep_kernel<<<n, 128, 0, s>>>(D, qkv, ld, a_raw, lda, b_raw, ldb_, (const __nv_bfloat16*)A_log, (const __nv_bfloat16*)dt_bias, beta, decay);
+    else delta_prep_kernel<<<n, 128, 0, s>>>(D, qkv, ld, a_raw, lda, b_raw, ldb_, (const float*)A_log, (const float*)dt_bias, beta, decay);
+    return launch_check(cudaGetLastError(), "delta_prep");
+}
+
+int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int ld, const float* beta, const float* decay, float* state,
+                      size_t slot_stride, float* o, cudaStream_t s) {
+    if (b.nseq <= 0) return WF_OK;
+    if (D.Hk <= 0 || D.H % D.Hk) { set_error("delta: %d heads over %d key heads", D.H, D.Hk); return WF_ERR_INVALID; }
+    dim3 grid(b.nseq, D.H, (D.dv + DR_COLS - 1) / DR_COLS);
+    const size_t smem = ((size_t)2 * DR_TT * D.d + DR_TT * DR_COLS + 2 * DR_TT) * sizeof(float);
+    const int threads = DR_COLS * DR_PARTS;
+    const int dpt = (D.d + DR_PARTS - 1) / DR_PARTS;
+    if (dpt <= 8) delta_rule_kernel<8><<<grid, threads, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o);
+    else if (dpt <= 16) delta_rule_kernel<16><<<grid, threads, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o);
+    else if (dpt <= 32) delta_rule_kernel<32><<<grid, threads, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o);
+    else if (dpt <= 64) delta_rule_kernel<64><<<grid, threads, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o);
+    else { set_error("delta: key dimension %d above the supported 256", D.d); return WF_ERR_UNSUPPORTED; }
+    return launch_check(cudaGetLastError(), "delta_rule");
+}
+
+int launch_delta_post(int dt, const DeltaDims& D, int n, const float* o, const void* w, float eps, const float* g, int ldg, void* y, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (dt == WF_BF16) delta_post_kernel<<<n, 128, 0, s>>>(D, o, (const __nv_bfloat16*)w, eps, g, ldg, (__nv_bfloat16*)y);
+    else delta_post_kernel<<<n, 128, 0, s>>>(D, o, (const float*)w, eps, g, ldg, (float*)y);
+    return launch_check(cudaGetLastError(), "delta_post");
+}
+
+}  // namespace seq
+}  // namespace wf

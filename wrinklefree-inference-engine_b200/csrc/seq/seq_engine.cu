@@ -1,0 +1,639 @@
+// Serving engine for layer-stack sequence models (include/wf_seq.h): resident weights laid out for the kernels, a paged cache pool shared by
+// all cached layers, fixed-size state slots (convolution tails, recurrent matrices), and the step function over a ragged batch of
+// prompt portions and single decoded tokens.  The host side decides WHAT runs in a step (scheduler, trace replay); everything that
+// computes is a kernel launched from here.
+#include "seq_kernels.cuh"
+#include "../pager.h"
+#include "wf_seq.h"
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <map>
+#include <string>
+#include <vector>
+
+using namespace wf;
+using namespace wf::seq;
+
+namespace {
+
+struct TensorSlot {
+    std::string name;
+    void* dst = nullptr;      // where the elements go (device)
+    size_t count = 0;
+    bool loaded = false;
+};
+
+struct LayerState {
+    wf_seq_layer c;
+    // weights (device, storage type)
+    void *norm1, *norm2, *norm1b, *norm2b, *canon1, *canon2;
+    void* wp = nullptr;       // fused input projections [np, W]
+    int np = 0;
+    void* wo = nullptr;       // [W, heads * vdim]
+    // latent attention
+    void *dkv_norm = nullptr, *uk = nullptr, *ukT = nullptr, *uv = nullptr;
+    long long cache_off = 0;  // element offset of this layer inside a cache page
+    // delta
+    void *conv_w = nullptr, *A_log = nullptr, *dt_bias = nullptr, *onorm = nullptr;
+    int C = 0;                // convolved channels
+    // routed feed-forward
+    void *router = nullptr, *correction = nullptr, *wgu = nullptr, *wd = nullptr;
+    // state slot offsets (floats)
+    size_t st_canon1 = 0, st_canon2 = 0, st_conv = 0, st_S = 0;
+};
+
+}  // namespace
+
+struct wf_seq_engine {
+    wf_seq_config cfg;
+    int dt = WF_BF16;
+    size_t esz = 2;
+    cudaStream_t stream = nullptr;
+    std::vector<LayerState> layers;
+    std::vector<TensorSlot> tensors;
+    std::map<std::string, int> tensor_index;
+    void *embed = nullptr, *final_norm = nullptr, *head = nullptr;
+    bool finalized = false;
+    // cache + state
+    PageTable pt;
+    std::vector<int32_t> h_len;       // [slots] tokens held
+    void* pool = nullptr;
+    long long page_stride = 0;        // elements per page
+    float* state = nullptr;
+    size_t slot_stride = 0;           // floats per slot
+    int32_t* d_block_table = nullptr;
+    // step metadata
+    int32_t *h_meta = nullptr, *d_meta = nullptr;
+    size_t meta_ints = 0;
+    // workspace
+    float *x = nullptr, *hn = nullptr, *y = nullptr, *proj = nullptr, *qr = nullptr, *qa = nullptr, *ov = nullptr, *qkvc = nullptr, *beta = nullptr,
+          *decay = nullptr, *od = nullptr, *z = nullptr, *wts = nullptr, *gu = nullptr, *yexp = nullptr;
+    void *h_t = nullptr, *qn = nullptr, *olat = nullptr, *og = nullptr, *hmid = nullptr, *xn = nullptr;
+    int32_t *ids = nullptr, *counts = nullptr, *plan_scratch = nullptr, *sorted_rows = nullptr, *pair_row = nullptr, *tile_group = nullptr;
+    int P = 0;                        // padded expert-row bound
+    float* logits = nullptr;
+    size_t logits_rows = 0;
+    float* d_uniform = nullptr;
+    int32_t* d_next = nullptr;
+    size_t sample_rows = 0;
+    float* layer_tap = nullptr;
+    int launches = 0;
+    size_t dev_bytes = 0;
+    std::vector<void*> allocs;
+};
+
+namespace {
+
+int dalloc_bytes(wf_seq_engine* e, void** p, size_t bytes) {
+    void* q = nullptr;
+    if (bytes == 0) bytes = 16;
+    bytes = (bytes + 255) / 256 * 256;
+    if (cuda_check(cudaMalloc(&q, bytes), "cudaMalloc")) return WF_ERR_CUDA;
+    e->allocs.push_back(q);
+    e->dev_bytes += bytes;
+    *p = q;
+    return WF_OK;
+}
+template <typename P>
+int dalloc_t(wf_seq_engine* e, P** p, size_t count) { return dalloc_bytes(e, (void**)p, count * e->esz); }   // storage-type elements
+template <typename P>
+int dalloc_n(wf_seq_engine* e, P** p, size_t count) { return dalloc_bytes(e, (void**)p, count * sizeof(P)); }
+
+void add_tensor(wf_seq_engine* e, const std::string& name, void* dst, size_t count) {
+    TensorSlot t;
+    t.name = name; t.dst = dst; t.count = count;
+    e->tensor_index[name] = (int)e->tensors.size();
+    e->tensors.push_back(t);
+}
+void* at(const wf_seq_engine* e, void* base, size_t elems) { return (char*)base + elems * e->esz; }
+
+int validate(const wf_seq_config& c, const wf_seq_layer* L) {
+    if (c.dtype != WF_SEQ_F32 && c.dtype != WF_SEQ_BF16) { set_error("wf_seq_create: dtype %d", c.dtype); return WF_ERR_INVALID; }
+    if (c.vocab <= 0 || c.width <= 0 || c.n_layers <= 0 || c.norm_groups <= 0 || c.width % c.norm_groups || c.canon_taps < 1) {
+        set_error("wf_seq_create: vocab %d width %d layers %d norm groups %d taps %d", c.vocab, c.width, c.n_layers, c.norm_groups, c.canon_taps);
+        return WF_ERR_INVALID;
+    }
+    if (c.page_size <= 0 || c.max_pages <= 0 || c.slots <= 0 || c.max_step_tokens <= 0) { set_error("wf_seq_create: page / slot / step sizes must be positive"); return WF_ERR_INVALID; }
+    for (int i = 0; i < c.n_layers; ++i) {
+        const wf_seq_layer& l = L[i];
+        if (l.heads <= 0 || l.dim <= 0 || l.vdim <= 0) { set_error("layer %d: heads / dim / vdim must be positive", i); return WF_ERR_INVALID; }
+        if (l.type == WF_SEQ_LATENT_ATTENTION) {
+            if (l.kv_rank <= 0 || l.rot_dim < 0 || l.window < 1 || l.rope_dims < 0 || l.rope_dims > l.rot_dim || (l.rope_dims & 1)) { set_error("layer %d: latent attention sizes", i); return WF_ERR_INVALID; }
+        } else if (l.type == WF_SEQ_DELTA) {
+            if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.conv < 1) { set_error("layer %d: delta sizes", i); return WF_ERR_INVALID; }
+        } else { set_error("layer %d: unknown mixer type %d", i, l.type); return WF_ERR_INVALID; }
+        if (l.has_ff) {
+            const int N = l.experts + l.identity;
+            if (l.experts < 0 || l.identity < 0 || N <= 0 || l.top < 1 || l.top > N || l.groups < 1 || N % l.groups || l.keep < 1 || l.keep > l.groups || (l.experts > 0 && l.ff <= 0)) {
+                set_error("layer %d: router sizes", i); return WF_ERR_INVALID;
+            }
+        }
+    }
+    return WF_OK;
+}
+
+struct StepView {
+    Batch b;
+    const int32_t* tokens;
+    const int32_t* want;
+};
+
+// host bookkeeping + one H2D copy of a step's index arrays
+int prepare_step(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t* counts, const int32_t* tokens, int nwant, const int32_t* want,
+                 StepView* v) {
+    const wf_seq_config& c = e->cfg;
+    if (!e->finalized) { set_error("wf_seq_step: weights are not finalized"); return WF_ERR_INVALID; }
+    if (nseq <= 0 || nseq > c.slots) { set_error("wf_seq_step: %d sequences (slots: %d)", nseq, c.slots); return WF_ERR_INVALID; }
+    int n = 0;
+    for (int i = 0; i < nseq; ++i) {
+        const int s = slots[i];
+        if (s < 0 || s >= c.slots || !e->pt.live[s]) { set_error("wf_seq_step: slot %d is not live", s); return WF_ERR_INVALID; }
+        for (int j = 0; j < i; ++j) if (slots[j] == s) { set_error("wf_seq_step: slot %d twice in one step", s); return WF_ERR_INVALID; }
+        if (counts[i] <= 0) { set_error("wf_seq_step: sequence %d brings %d tokens", i, counts[i]); return WF_ERR_INVALID; }
+        n += counts[i];
+    }
+    if (n > c.max_step_tokens) { set_error("wf_seq_step: %d tokens in one step (limit %d)", n, c.max_step_tokens); return WF_ERR_INVALID; }
+    if (nwant < 0 || nwant > n) { set_error("wf_seq_step: %d wanted rows of %d tokens", nwant, n); return WF_ERR_INVALID; }
+    for (int j = 0; j < nwant; ++j) if (want[j] < 0 || want[j] >= n) { set_error("wf_seq_step: wanted row %d out of range", want[j]); return WF_ERR_INVALID; }
+    if (tokens) for (int i = 0; i < n; ++i) if (tokens[i] < 0 || tokens[i] >= c.vocab) { set_error("wf_seq_step: token id %d outside the vocabulary", tokens[i]); return WF_ERR_INVALID; }
+    // pages for the new tokens (all or nothing)
+    for (int i = 0; i < nseq; ++i) {
+        if (!e->pt.ensure(slots[i], e->h_len[slots[i]] + counts[i])) {
+            set_error("wf_seq_step: cache pool exhausted (%d pages of %d tokens, %d free)", c.max_pages, c.page_size, (int)e->pt.free_pages.size());
+            for (int j = 0; j <= i; ++j) e->pt.truncate(slots[j], e->h_len[slots[j]]);
+            return WF_ERR_INVALID;
+        }
+    }
+    int32_t* m = e->h_meta;
+    const size_t T = c.max_step_tokens, S = c.slots;
+    int32_t *m_tok = m, *m_tseq = m + T, *m_tpos = m + 2 * T, *m_start = m + 3 * T, *m_len = m_start + S, *m_pos0 = m_len + S, *m_slot = m_pos0 + S,
+            *m_want = m_slot + S;
+    int at_ = 0;
+    for (int i = 0; i < nseq; ++i) {
+        m_start[i] = at_; m_len[i] = counts[i]; m_pos0[i] = e->h_len[slots[i]]; m_slot[i] = slots[i];
+        for (int k = 0; k < counts[i]; ++k) { m_tok[at_] = tokens ? tokens[at_] : 0; m_tseq[at_] = i; m_tpos[at_] = m_pos0[i] + k; ++at_; }
+    }
+    for (int j = 0; j < nwant; ++j) m_want[j] = want[j];
+    if (cuda_check(cudaMemcpyAsync(e->d_meta, m, e->meta_ints * 4, cudaMemcpyHostToDevice, e->stream), "step metadata H2D")) return WF_ERR_CUDA;
+    if (e->pt.dirty) {
+        std::vector<int32_t> tmp(e->pt.table);
+        for (auto& p : tmp) if (p < 0) p = 0;      // a stale lookup can never leave the pool
+        if (cuda_check(cudaMemcpyAsync(e->d_block_table, tmp.data(), tmp.size() * 4, cudaMemcpyHostToDevice, e->stream), "block table H2D")) return WF_ERR_CUDA;
+        if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) return WF_ERR_CUDA;   // tmp is pageable
+        e->pt.dirty = false;
+    }
+    int32_t* d = e->d_meta;
+    v->tokens = d;
+    v->b.n = n; v->b.nseq = nseq;
+    v->b.tok_seq = d + T; v->b.tok_pos = d + 2 * T;
+    v->b.seq_start = d + 3 * T; v->b.seq_len = d + 3 * T + S; v->b.seq_pos0 = d + 3 * T + 2 * S; v->b.seq_slot = d + 3 * T + 3 * S;
+    v->want = d + 3 * T + 4 * S;
+    return WF_OK;
+}
+
+void commit_lengths(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t* counts) {
+    for (int i = 0; i < nseq; ++i) e->h_len[slots[i]] += counts[i];
+}
+
+GemmArgs lin(const void* A, int a_f32, int lda, const void* B, int ldb, void* C, int c_f32, int ldc, int M, int N, int K) {
+    GemmArgs g;
+    g.A = A; g.a_f32 = a_f32; g.lda = lda; g.B = B; g.ldb = ldb; g.C = C; g.c_f32 = c_f32; g.ldc = ldc; g.M = M; g.N = N; g.K = K;
+    return g;
+}
+
+// h (post-convolution input, storage type [n, W]) -> y float [n, W]
+int run_latent(wf_seq_engine* e, LayerState& L, const Batch& b) {
+    const wf_seq_layer& c = L.c;
+    const int W = e->cfg.width, n = b.n, H = c.heads, per = c.dim + c.rot_dim, nq = H * per, nkv = c.kv_rank + c.rot_dim, nv = H * c.vdim;
+    cudaStream_t s = e->stream;
+    int rc;
+    LatentDims D{H, c.dim, c.rot_dim, c.vdim, c.kv_rank, c.scale, c.rope_base, c.rope_dims, c.window};
+    PagedCache pc{e->pool, e->page_stride, L.cache_off, e->cfg.page_size, e->d_block_table, e->pt.max_blocks};
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q | dkv | g]
+    if ((rc = launch_latent_q_prep(e->dt, b, D, e->proj, L.np, e->qn, e->qr, s))) return rc;
+    if ((rc = launch_latent_kv_write(e->dt, b, D, e->proj + nq, L.np, L.dkv_norm, e->cfg.eps, pc, s))) return rc;
+    {   // qa[i, h, :] = W_uk[h]^T qn[i, h, :]
+        GemmArgs g = lin(e->qn, 0, H * c.dim, L.ukT, c.dim, e->qa, 1, H * c.kv_rank, n, c.kv_rank, c.dim);
+        g.batch = H; g.sA = c.dim; g.sB = (long long)c.kv_rank * c.dim; g.sC = c.kv_rank;
+        if ((rc = launch_gemm(e->dt, g, s))) return rc;
+    }
+    if ((rc = launch_latent_attn(e->dt, b, D, e->qa, e->qr, pc, e->olat, s))) return rc;
+    {   // ov[i, h, :] = W_uv[h] olat[i, h, :]
+        GemmArgs g = lin(e->olat, 0, H * c.kv_rank, L.uv, c.kv_rank, e->ov, 1, nv, n, c.vdim, c.kv_rank);
+        g.batch = H; g.sA = c.kv_rank; g.sB = (long long)c.vdim * c.kv_rank; g.sC = c.vdim;
+        if ((rc = launch_gemm(e->dt, g, s))) return rc;
+    }
+    if ((rc = launch_gate_mul(e->dt, e->ov, nv, e->proj + nq + nkv, L.np, 0, n, nv, e->og, nv, s))) return rc;
+    return launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
+}
+
+int run_delta(wf_seq_engine* e, LayerState& L, const Batch& b) {
+    const wf_seq_layer& c = L.c;
+    const int W = e->cfg.width, n = b.n, H = c.heads, nv = H * c.vdim, C = L.C;
+    cudaStream_t s = e->stream;
+    int rc;
+    DeltaDims D{H, c.kv_heads, c.dim, c.vdim};
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q | k | v | g | b | a]
+    float* st_conv = e->state + L.st_conv;
+    if ((rc = launch_causal_taps(e->dt, b, e->proj, L.np, L.conv_w, c.conv, C, st_conv, e->slot_stride, 0, 1, nullptr, 0, e->qkvc, C, s))) return rc;
+    if ((rc = launch_taps_state(b, e->proj, L.np, c.conv, C, st_conv, e->slot_stride, s))) return rc;
+    const float* g_raw = e->proj + C;
+    const float* b_raw = g_raw + nv;
+    const float* a_raw = b_raw + H;
+    if ((rc = launch_delta_prep(e->dt, D, n, e->qkvc, C, a_raw, L.np, b_raw, L.np, L.A_log, L.dt_bias, e->beta, e->decay, s))) return rc;
+    if ((rc = launch_delta_rule(b, D, e->qkvc, C, e->beta, e->decay, e->state + L.st_S, e->slot_stride, e->od, s))) return rc;
+    if ((rc = launch_delta_post(e->dt, D, n, e->od, L.onorm, e->cfg.eps, g_raw, L.np, e->og, s))) return rc;
+    return launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
+}
+
+int run_mixer(wf_seq_engine* e, LayerState& L, const Batch& b) {
+    return L.c.type == WF_SEQ_LATENT_ATTENTION ? run_latent(e, L, b) : run_delta(e, L, b);
+}
+
+int run_ff(wf_seq_engine* e, LayerState& L, const Batch& b) {
+    const wf_seq_layer& c = L.c;
+    const int W = e->cfg.width, n = b.n, N = c.experts + c.identity;
+    cudaStream_t s = e->stream;
+    int rc;
+    RouterDims R{c.experts, c.identity, c.top, c.groups, c.keep};
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.router, W, e->z, 1, N, n, N, W), s))) return rc;
+    if (c.experts > 0 && cuda_check(cudaMemsetAsync(e->counts, 0, (size_t)c.experts * 4, s), "counts")) return WF_ERR_CUDA;
+    if ((rc = launch_moe_route(e->dt, R, n, e->z, N, L.correction, e->ids, e->wts, e->counts, s))) return rc;
+    if (c.experts > 0) {
+        const int P = (n * c.top + GEMM_BM - 1) / GEMM_BM * GEMM_BM + c.experts * GEMM_BM;
+        if ((rc = launch_moe_plan(R, n, e->ids, e->counts, e->plan_scratch, e->sorted_rows, e->pair_row, e->tile_group, P, s))) return rc;
+        GemmArgs g = lin(e->h_t, 0, W, L.wgu, W, e->gu, 1, 2 * c.ff, P, 2 * c.ff, W);
+        g.tile_group = e->tile_group; g.group_stride = (long long)2 * c.ff * W; g.a_rows = e->sorted_rows;
+        if ((rc = launch_gemm(e->dt, g, s))) return rc;
+        if ((rc = launch_silu_mul(e->dt, e->gu, P, c.ff, e->tile_group, e->hmid, s))) return rc;
+        GemmArgs g2 = lin(e->hmid, 0, c.ff, L.wd, c.ff, e->yexp, 1, W, P, W, c.ff);
+        g2.tile_group = e->tile_group; g2.group_stride = (long long)W * c.ff;
+        if ((rc = launch_gemm(e->dt, g2, s))) return rc;
+    }
+    return launch_moe_combine(e->dt, R, n, W, e->ids, e->wts, e->pair_row, e->yexp, e->h_t, e->y, s);
+}
+
+// norm -> input convolution (state rolled forward) -> e->h_t
+int run_input(wf_seq_engine* e, const Batch& b, const void* norm_w, const void* canon_w, size_t st_off) {
+    const int W = e->cfg.width;
+    cudaStream_t s = e->stream;
+    int rc;
+    if ((rc = launch_group_rmsnorm(e->dt, e->x, W, norm_w, e->cfg.norm_groups, e->cfg.eps, b.n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s))) return rc;
+    if ((rc = launch_causal_taps(e->dt, b, e->hn, W, canon_w, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, 1, 0, e->h_t, W, nullptr, 0, s))) return rc;
+    return launch_taps_state(b, e->hn, W, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, s);
+}
+
+int run_layers(wf_seq_engine* e, const StepView& v) {
+    const int W = e->cfg.width, n = v.b.n;
+    cudaStream_t s = e->stream;
+    int rc;
+    if ((rc = launch_embed_f32(e->dt, e->embed, v.tokens, n, W, e->x, s))) return rc;
+    for (int li = 0; li < e->cfg.n_layers; ++li) {
+        LayerState& L = e->layers[li];
+        if ((rc = run_input(e, v.b, L.norm1, L.canon1, L.st_canon1))) return rc;
+        if ((rc = run_mixer(e, L, v.b))) return rc;
+        if ((rc = launch_group_rmsnorm(e->dt, e->y, W, L.norm1b, e->cfg.norm_groups, e->cfg.eps, n, W, e->x, e->x, W, nullptr, 0, nullptr, s))) return rc;
+        if (L.c.has_ff) {
+            if ((rc = run_input(e, v.b, L.norm2, L.canon2, L.st_canon2))) return rc;
+            if ((rc = run_ff(e, L, v.b))) return rc;
+            if ((rc = launch_group_rmsnorm(e->dt, e->y, W, L.norm2b, e->cfg.norm_groups, e->cfg.eps, n, W, e->x, e->x, W, nullptr, 0, nullptr, s))) return rc;
+        }
+        if (e->layer_tap) {
+            if (cuda_check(cudaMemcpyAsync(e->layer_tap + (size_t)li * n * W, e->x, (size_t)n * W * 4, cudaMemcpyDeviceToHost, s), "layer tap")) return WF_ERR_CUDA;
+        }
+    }
+    return WF_OK;
+}
+
+int ensure_logits(wf_seq_engine* e, size_t rows) {
+    if (rows <= e->logits_rows) return WF_OK;
+    if (e->logits) { cudaFree(e->logits); e->dev_bytes -= e->logits_rows * e->cfg.vocab * 4; }
+    e->logits = nullptr; e->logits_rows = 0;
+    if (cuda_check(cudaMalloc((void**)&e->logits, rows * e->cfg.vocab * 4), "cudaMalloc logits")) return WF_ERR_CUDA;
+    e->logits_rows = rows;
+    e->dev_bytes += rows * e->cfg.vocab * 4;
+    return WF_OK;
+}
+
+int run_head(wf_seq_engine* e, const StepView& v, int nwant) {
+    if (nwant <= 0) return WF_OK;
+    const int W = e->cfg.width;
+    int rc;
+    if ((rc = ensure_logits(e, nwant))) return rc;
+    if ((rc = launch_group_rmsnorm(e->dt, e->x, W, e->final_norm, e->cfg.norm_groups, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream))) return rc;
+    return launch_gemm(e->dt, lin(e->xn, 0, W, e->head, W, e->logits, 1, e->cfg.vocab, nwant, e->cfg.vocab, W), e->stream);
+}
+
+}  // namespace
+
+extern "C" int wf_seq_available(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) { cudaGetLastError(); return 0; }
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
+    return major == 10 ? 1 : 0;
+}
+
+extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layers, wf_seq_engine** out) {
+    if (!cfg || !layers || !out) { set_error("wf_seq_create: null argument"); return WF_ERR_INVALID; }
+    if (int rc = validate(*cfg, layers)) return rc;
+    if (!wf_seq_available()) { set_error("wf_seq_create: no compute-capability-10.x device"); return WF_ERR_UNSUPPORTED; }
+    wf_seq_engine* e = new wf_seq_engine();
+    e->cfg = *cfg;
+    e->dt = cfg->dtype == WF_SEQ_F32 ? WF_F32 : WF_BF16;
+    e->esz = e->dt == WF_F32 ? 4 : 2;
+    const wf_seq_config& c = e->cfg;
+    const int W = c.width, T = c.max_step_tokens, taps = c.canon_taps;
+    int rc = WF_OK;
+#define TRY(x) do { if ((rc = (x))) { wf_seq_destroy(e); return rc; } } while (0)
+    if (cuda_check(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking), "stream")) { delete e; return WF_ERR_CUDA; }
+    TRY(dalloc_t(e, &e->embed, (size_t)c.vocab * W));
+    TRY(dalloc_t(e, &e->final_norm, W));
+    TRY(dalloc_t(e, &e->head, (size_t)c.vocab * W));
+    add_tensor(e, "embed", e->embed, (size_t)c.vocab * W);
+    add_tensor(e, "final.norm", e->final_norm, W);
+    add_tensor(e, "head", e->head, (size_t)c.vocab * W);
+    // maxima over layers for the shared workspaces
+    size_t max_np = 1, max_hd = 1, max_hr = 1, max_hrot = 1, max_hv = 1, max_C = 1, max_H = 1, max_N = 1, max_top = 1, max_E = 1, max_ff = 1;
+    long long cache_elems = 0;
+    size_t st = 0;
+    e->layers.resize(c.n_layers);
+    for (int li = 0; li < c.n_layers; ++li) {
+        LayerState& L = e->layers[li];
+        L.c = layers[li];
+        const wf_seq_layer& l = L.c;
+        const std::string p = "l" + std::to_string(li) + ".";
+        void** norms[4] = {&L.norm1, &L.norm1b, &L.norm2, &L.norm2b};
+        const char* norm_names[4] = {"norm1", "norm1b", "norm2", "norm2b"};
+        for (int k = 0; k < (l.has_ff ? 4 : 2); ++k) { TRY(dalloc_t(e, norms[k], W)); add_tensor(e, p + norm_names[k], *norms[k], W); }
+        TRY(dalloc_t(e, &L.canon1, (size_t)W * taps)); add_tensor(e, p + "canon1", L.canon1, (size_t)W * taps);
+        L.st_canon1 = st; st += (size_t)(taps - 1) * W;
+        if (l.has_ff) {
+            TRY(dalloc_t(e, &L.canon2, (size_t)W * taps)); add_tensor(e, p + "canon2", L.canon2, (size_t)W * taps);
+            L.st_canon2 = st; st += (size_t)(taps - 1) * W;
+        }
+        const size_t nv = (size_t)l.heads * l.vdim;
+        TRY(dalloc_t(e, &L.wo, (size_t)W * nv)); add_tensor(e, p + "mix.o", L.wo, (size_t)W * nv);
+        if (l.type == WF_SEQ_LATENT_ATTENTION) {
+            const size_t nq = (size_t)l.heads * (l.dim + l.rot_dim), nkv = l.kv_rank + l.rot_dim;
+            L.np = (int)(nq + nkv + nv);
+            TRY(dalloc_t(e, &L.wp, (size_t)L.np * W));
+            add_tensor(e, p + "mix.q", L.wp, nq * W);
+            add_tensor(e, p + "mix.dkv", at(e, L.wp, nq * W), nkv * W);
+            add_tensor(e, p + "mix.g", at(e, L.wp, (nq + nkv) * W), nv * W);
+            TRY(dalloc_t(e, &L.dkv_norm, l.kv_rank)); add_tensor(e, p + "mix.dkv.norm", L.dkv_norm, l.kv_rank);
+            TRY(dalloc_t(e, &L.uk, (size_t)l.heads * l.dim * l.kv_rank)); add_tensor(e, p + "mix.uk", L.uk, (size_t)l.heads * l.dim * l.kv_rank);
+            TRY(dalloc_t(e, &L.ukT, (size_t)l.heads * l.dim * l.kv_rank));
+            TRY(dalloc_t(e, &L.uv, nv * l.kv_rank)); add_tensor(e, p + "mix.uv", L.uv, nv * l.kv_rank);
+            L.cache_off = cache_elems;
+            cache_elems += (long long)c.page_size * nkv;
+            max_hd = std::max(max_hd, (size_t)l.heads * l.dim); max_hr = std::max(max_hr, (size_t)l.heads * l.kv_rank);
+            max_hrot = std::max(max_hrot, (size_t)l.heads * std::max(l.rot_dim, 1));
+        } else {
+            const size_t nqk = (size_t)l.kv_heads * l.dim;
+            L.C = (int)(2 * nqk + nv);
+            L.np = (int)(L.C + nv + 2 * l.heads);
+            TRY(dalloc_t(e, &L.wp, (size_t)L.np * W));
+            add_tensor(e, p + "mix.q", L.wp, nqk * W);
+            add_tensor(e, p + "mix.k", at(e, L.wp, nqk * W), nqk * W);
+            add_tensor(e, p + "mix.v", at(e, L.wp, 2 * nqk * W), nv * W);
+            add_tensor(e, p + "mix.g", at(e, L.wp, (size_t)L.C * W), nv * W);
+            add_tensor(e, p + "mix.b", at(e, L.wp, ((size_t)L.C + nv) * W), (size_t)l.heads * W);
+            add_tensor(e, p + "mix.a", at(e, L.wp, ((size_t)L.C + nv + l.heads) * W), (size_t)l.heads * W);
+            TRY(dalloc_t(e, &L.conv_w, (size_t)L.C * l.conv));
+            add_tensor(e, p + "mix.q.conv", L.conv_w, nqk * l.conv);
+            add_tensor(e, p + "mix.k.conv", at(e, L.conv_w, nqk * l.conv), nqk * l.conv);
+            add_tensor(e, p + "mix.v.conv", at(e, L.conv_w, 2 * nqk * l.conv), nv * l.conv);
+            TRY(dalloc_t(e, &L.A_log, l.heads)); add_tensor(e, p + "mix.A_log", L.A_log, l.heads);
+            TRY(dalloc_t(e, &L.dt_bias, l.heads)); add_tensor(e, p + "mix.dt_bias", L.dt_bias, l.heads);
+            TRY(dalloc_t(e, &L.onorm, l.vdim)); add_tensor(e, p + "mix.norm", L.onorm, l.vdim);
+            L.st_conv = st; st += (size_t)(l.conv - 1) * L.C;
+            L.st_S = st; st += (size_t)l.heads * l.dim * l.vdim;
+            max_C = std::max(max_C, (size_t)L.C);
+        }
+        max_np = std::max(max_np, (size_t)L.np); max_hv = std::max(max_hv, nv); max_H = std::max(max_H, (size_t)l.heads);
+        if (l.has_ff) {
+            const size_t N = l.experts + l.identity;
+            TRY(dalloc_t(e, &L.router, N * W)); add_tensor(e, p + "mlp.router", L.router, N * W);
+            TRY(dalloc_t(e, &L.correction, N)); add_tensor(e, p + "mlp.correction", L.correction, N);
+            if (l.experts > 0) {
+                TRY(dalloc_t(e, &L.wgu, (size_t)l.experts * 2 * l.ff * W));
+                TRY(dalloc_t(e, &L.wd, (size_t)l.experts * W * l.ff));
+                for (int x = 0; x < l.experts; ++x) {
+                    const std::string ep = p + "mlp.e" + std::to_string(x) + ".";
+                    add_tensor(e, ep + "gate", at(e, L.wgu, (size_t)x * 2 * l.ff * W), (size_t)l.ff * W);
+                    add_tensor(e, ep + "up", at(e, L.wgu, ((size_t)x * 2 + 1) * l.ff * W), (size_t)l.ff * W);
+                    add_tensor(e, ep + "down", at(e, L.wd, (size_t)x * W * l.ff), (size_t)W * l.ff);
+                }
+            }
+            max_N = std::max(max_N, N); max_top = std::max(max_top, (size_t)l.top); max_E = std::max(max_E, (size_t)std::max(l.experts, 1));
+            max_ff = std::max(max_ff, (size_t)std::max(l.ff, 1));
+            const int P = (T * l.top + GEMM_BM - 1) / GEMM_BM * GEMM_BM + l.experts * GEMM_BM;
+            e->P = std::max(e->P, P);
+        }
+    }
+    // cache pool and state slots
+    e->page_stride = cache_elems;
+    TRY(dalloc_t(e, &e->pool, (size_t)std::max<long long>(cache_elems, 1) * c.max_pages));
+    e->slot_stride = st ? st : 1;
+    TRY(dalloc_n(e, &e->state, e->slot_stride * c.slots));
+    const int max_blocks = c.max_pages;        // one sequence may hold the whole pool
+    e->pt.init(c.max_pages, c.page_size, c.slots, max_blocks);
+    e->h_len.assign(c.slots, 0);
+    TRY(dalloc_n(e, &e->d_block_table, (size_t)c.slots * max_blocks));
+    e->meta_ints = (size_t)4 * T + (size_t)4 * c.slots;
+    TRY(dalloc_n(e, &e->d_meta, e->meta_ints));
+    if (cuda_check(cudaMallocHost((void**)&e->h_meta, e->meta_ints * 4), "pinned metadata")) { wf_seq_destroy(e); return WF_ERR_CUDA; }
+    // workspaces
+    TRY(dalloc_n(e, &e->x, (size_t)T * W)); TRY(dalloc_n(e, &e->hn, (size_t)T * W)); TRY(dalloc_n(e, &e->y, (size_t)T * W));
+    TRY(dalloc_t(e, &e->h_t, (size_t)T * W)); TRY(dalloc_t(e, &e->xn, (size_t)T * W));
+    TRY(dalloc_n(e, &e->proj, (size_t)T * max_np));
+    TRY(dalloc_t(e, &e->qn, (size_t)T * max_hd)); TRY(dalloc_n(e, &e->qr, (size_t)T * max_hrot)); TRY(dalloc_n(e, &e->qa, (size_t)T * max_hr));
+    TRY(dalloc_t(e, &e->olat, (size_t)T * max_hr)); TRY(dalloc_n(e, &e->ov, (size_t)T * max_hv)); TRY(dalloc_t(e, &e->og, (size_t)T * max_hv));
+    TRY(dalloc_n(e, &e->qkvc, (size_t)T * max_C)); TRY(dalloc_n(e, &e->beta, (size_t)T * max_H)); TRY(dalloc_n(e, &e->decay, (size_t)T * max_H));
+    TRY(dalloc_n(e, &e->od, (size_t)T * max_hv));
+    TRY(dalloc_n(e, &e->z, (size_t)T * max_N)); TRY(dalloc_n(e, &e->ids, (size_t)T * max_top)); TRY(dalloc_n(e, &e->wts, (size_t)T * max_top));
+    TRY(dalloc_n(e, &e->pair_row, (size_t)T * max_top)); TRY(dalloc_n(e, &e->counts, max_E)); TRY(dalloc_n(e, &e->plan_scratch, 2 * max_E + 1));
+    const size_t P = e->P ? e->P : GEMM_BM;
+    TRY(dalloc_n(e, &e->sorted_rows, P)); TRY(dalloc_n(e, &e->tile_group, P / GEMM_BM));
+    TRY(dalloc_n(e, &e->gu, P * 2 * max_ff)); TRY(dalloc_t(e, &e->hmid, P * max_ff)); TRY(dalloc_n(e, &e->yexp, P * W));
+#undef TRY
+    if (cuda_check(cudaMemsetAsync(e->state, 0, e->slot_stride * c.slots * 4, e->stream), "state")) { wf_seq_destroy(e); return WF_ERR_CUDA; }
+    if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) { wf_seq_destroy(e); return WF_ERR_CUDA; }
+    *out = e;
+    return WF_OK;
+}
+
+extern "C" void wf_seq_destroy(wf_seq_engine* e) {
+    if (!e) return;
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    for (void* p : e->allocs) cudaFree(p);
+    if (e->logits) cudaFree(e->logits);
+    if (e->d_uniform) cudaFree(e->d_uniform);
+    if (e->d_next) cudaFree(e->d_next);
+    if (e->h_meta) cudaFreeHost(e->h_meta);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+extern "C" size_t wf_seq_device_bytes(const wf_seq_engine* e) { return e ? e->dev_bytes : 0; }
+extern "C" int wf_seq_tensor_count(const wf_seq_engine* e) { return e ? (int)e->tensors.size() : 0; }
+extern "C" const char* wf_seq_tensor_name(const wf_seq_engine* e, int i, size_t* count, int* loaded) {
+    if (!e || i < 0 || i >= (int)e->tensors.size()) return nullptr;
+    if (count) *count = e->tensors[i].count;
+    if (loaded) *loaded = e->tensors[i].loaded ? 1 : 0;
+    return e->tensors[i].name.c_str();
+}
+
+extern "C" int wf_seq_set_tensor(wf_seq_engine* e, const char* name, const void* data, size_t count, int is_host) {
+    if (!e || !name || !data) { set_error("wf_seq_set_tensor: null argument"); return WF_ERR_INVALID; }
+    auto it = e->tensor_index.find(name);
+    if (it == e->tensor_index.end()) { set_error("wf_seq_set_tensor: this model has no tensor '%s'", name); return WF_ERR_INVALID; }
+    TensorSlot& t = e->tensors[it->second];
+    if (count != t.count) { set_error("wf_seq_set_tensor: '%s' holds %zu elements, expected %zu", name, count, t.count); return WF_ERR_INVALID; }
+    if (cuda_check(cudaMemcpyAsync(t.dst, data, count * e->esz, is_host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice, e->stream), "tensor upload")) return WF_ERR_CUDA;
+    if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) return WF_ERR_CUDA;
+    t.loaded = true;
+    e->finalized = false;
+    return WF_OK;
+}
+
+extern "C" int wf_seq_finalize(wf_seq_engine* e) {
+    if (!e) return WF_ERR_INVALID;
+    for (const TensorSlot& t : e->tensors)
+        if (!t.loaded) { set_error("wf_seq_finalize: tensor '%s' was not loaded", t.name.c_str()); return WF_ERR_INVALID; }
+    for (LayerState& L : e->layers)
+        if (L.c.type == WF_SEQ_LATENT_ATTENTION)      // W_uk per head [dim, kv_rank] -> [kv_rank, dim]: the weight of q -> W_uk^T q
+            if (int rc = launch_transpose_heads(e->dt, L.uk, L.c.heads, L.c.dim, L.c.kv_rank, L.ukT, e->stream)) return rc;
+    if (cuda_check(cudaStreamSynchronize(e->stream), "finalize")) return WF_ERR_CUDA;
+    e->finalized = true;
+    return WF_OK;
+}
+
+extern "C" int wf_seq_admit(wf_seq_engine* e, int* slot) {
+    if (!e || !slot) return WF_ERR_INVALID;
+    const int s = e->pt.acquire_slot();
+    *slot = s;
+    if (s < 0) return WF_OK;
+    e->h_len[s] = 0;
+    // a slot that is used again must not carry the previous sequence's convolution tails or recurrent state
+    if (cuda_check(cudaMemsetAsync(e->state + (size_t)s * e->slot_stride, 0, e->slot_stride * 4, e->stream), "state reset")) return WF_ERR_CUDA;
+    return WF_OK;
+}
+
+extern "C" int wf_seq_release(wf_seq_engine* e, int slot) {
+    if (!e || slot < 0 || slot >= e->cfg.slots || !e->pt.live[slot]) { set_error("wf_seq_release: slot %d is not live", slot); return WF_ERR_INVALID; }
+    e->pt.release_slot(slot);
+    e->h_len[slot] = 0;
+    return WF_OK;
+}
+
+extern "C" int wf_seq_length(const wf_seq_engine* e, int slot) { return (e && slot >= 0 && slot < e->cfg.slots) ? e->h_len[slot] : -1; }
+extern "C" int wf_seq_free_pages(const wf_seq_engine* e) { return e ? (int)e->pt.free_pages.size() : 0; }
+extern "C" int wf_seq_free_slots(const wf_seq_engine* e) { return e ? (int)e->pt.free_slots.size() : 0; }
+extern "C" void* wf_seq_logits_device(wf_seq_engine* e) { return e ? e->logits : nullptr; }
+extern "C" int wf_seq_launches_last_step(const wf_seq_engine* e) { return e ? e->launches : 0; }
+extern "C" int wf_seq_set_layer_tap(wf_seq_engine* e, float* host) { if (!e) return WF_ERR_INVALID; e->layer_tap = host; return WF_OK; }
+
+extern "C" int wf_seq_step(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t* counts, const int32_t* tokens, int nwant,
+                           const int32_t* want, float* logits_host) {
+    if (!e || !slots || !counts || !tokens || (nwant > 0 && !want)) { set_error("wf_seq_step: null argument"); return WF_ERR_INVALID; }
+    StepView v;
+    int rc;
+    if ((rc = prepare_step(e, nseq, slots, counts, tokens, nwant, want, &v))) return rc;
+    const long long l0 = launch_count();
+    if ((rc = run_layers(e, v))) return rc;
+    if ((rc = run_head(e, v, nwant))) return rc;
+    e->launches = (int)(launch_count() - l0);
+    if (logits_host && nwant > 0)
+        if (cuda_check(cudaMemcpyAsync(logits_host, e->logits, (size_t)nwant * e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream), "logits D2H")) return WF_ERR_CUDA;
+    if (cuda_check(cudaStreamSynchronize(e->stream), "wf_seq_step")) return WF_ERR_CUDA;
+    commit_lengths(e, nseq, slots, counts);
+    return WF_OK;
+}
+
+extern "C" int wf_seq_sample(wf_seq_engine* e, int nwant, float temperature, int top_k, float top_p, const float* uniforms_host, int32_t* next_host) {
+    if (!e || !next_host || nwant <= 0 || (size_t)nwant > e->logits_rows) { set_error("wf_seq_sample: no logits for %d rows", nwant); return WF_ERR_INVALID; }
+    if ((size_t)nwant > e->sample_rows) {
+        if (e->d_uniform) cudaFree(e->d_uniform);
+        if (e->d_next) cudaFree(e->d_next);
+        e->d_uniform = nullptr; e->d_next = nullptr; e->sample_rows = 0;
+        if (cuda_check(cudaMalloc((void**)&e->d_uniform, (size_t)nwant * 4), "cudaMalloc")) return WF_ERR_CUDA;
+        if (cuda_check(cudaMalloc((void**)&e->d_next, (size_t)nwant * 4), "cudaMalloc")) return WF_ERR_CUDA;
+        e->sample_rows = nwant;
+    }
+    if (temperature > 0.f) {
+        if (!uniforms_host) { set_error("wf_seq_sample: uniforms required when temperature > 0"); return WF_ERR_INVALID; }
+        if (cuda_check(cudaMemcpyAsync(e->d_uniform, uniforms_host, (size_t)nwant * 4, cudaMemcpyHostToDevice, e->stream), "uniforms H2D")) return WF_ERR_CUDA;
+    }
+    if (int rc = launch_sample(e->logits, nwant, e->cfg.vocab, temperature, top_k, top_p, e->d_uniform, e->d_next, e->stream)) return rc;
+    if (cuda_check(cudaMemcpyAsync(next_host, e->d_next, (size_t)nwant * 4, cudaMemcpyDeviceToHost, e->stream), "next D2H")) return WF_ERR_CUDA;
+    return cuda_check(cudaStreamSynchronize(e->stream), "wf_seq_sample");
+}
+
+extern "C" int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, const int32_t* slots, const int32_t* counts, const float* in_host,
+                               float* out_host) {
+    if (!e || !slots || !counts || !in_host || !out_host || layer < 0 || layer >= e->cfg.n_layers) { set_error("wf_seq_run_part: bad argument"); return WF_ERR_INVALID; }
+    StepView v;
+    int rc;
+    if ((rc = prepare_step(e, nseq, slots, counts, nullptr, 0, nullptr, &v))) return rc;
+    LayerState& L = e->layers[layer];
+    const int W = e->cfg.width, n = v.b.n;
+    cudaStream_t s = e->stream;
+    const size_t bytes = (size_t)n * W * 4;
+    float* result = e->y;
+    if (part == 0) {
+        if (cuda_check(cudaMemcpyAsync(e->x, in_host, bytes, cudaMemcpyHostToDevice, s), "in")) return WF_ERR_CUDA;
+        rc = launch_group_rmsnorm(e->dt, e->x, W, L.norm1, e->cfg.norm_groups, e->cfg.eps, n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s);
+        result = e->hn;
+    } else if (part == 1 || part == 4) {
+        if (part == 4 && !L.c.has_ff) { set_error("wf_seq_run_part: layer %d has no feed-forward", layer); return WF_ERR_INVALID; }
+        if (cuda_check(cudaMemcpyAsync(e->hn, in_host, bytes, cudaMemcpyHostToDevice, s), "in")) return WF_ERR_CUDA;
+        const size_t off = part == 1 ? L.st_canon1 : L.st_canon2;
+        rc = launch_causal_taps(e->dt, v.b, e->hn, W, part == 1 ? L.canon1 : L.canon2, e->cfg.canon_taps, W, e->state + off, e->slot_stride, 1, 0, nullptr, 0, e->y, W, s);
+        if (!rc) rc = launch_taps_state(v.b, e->hn, W, e->cfg.canon_taps, W, e->state + off, e->slot_stride, s);
+    } else if (part == 2 || part == 3) {
+        if (part == 3 && !L.c.has_ff) { set_error("wf_seq_run_part: layer %d has no feed-forward", layer); return WF_ERR_INVALID; }
+        if (cuda_check(cudaMemcpyAsync(e->hn, in_host, bytes, cudaMemcpyHostToDevice, s), "in")) return WF_ERR_CUDA;
+        // round the given rows to the storage type exactly as the input convolution's output would be
+        rc = launch_gate_mul(e->dt, e->hn, W, e->hn, W, 2, n, W, e->h_t, W, s);
+        if (!rc) rc = part == 2 ? run_mixer(e, L, v.b) : run_ff(e, L, v.b);
+    } else { set_error("wf_seq_run_part: unknown part %d", part); return WF_ERR_INVALID; }
+    if (rc) return rc;
+    if (cuda_check(cudaMemcpyAsync(out_host, result, bytes, cudaMemcpyDeviceToHost, s), "out")) return WF_ERR_CUDA;
+    if (cuda_check(cudaStreamSynchronize(s), "wf_seq_run_part")) return WF_ERR_CUDA;
+    commit_lengths(e, nseq, slots, counts);
+    return WF_OK;
+}
+
+extern "C" int wf_seq_time_step(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t* counts, int iters, float* ms_out) {
+    if (!e || !slots || !counts || !ms_out || iters <= 0) { set_error("wf_seq_time_step: bad argument"); return WF_ERR_INVALID; }
+    int n = 0;
+    for (int i = 0; i < nseq; ++i) n += counts[i];
+    if (n <= 0 || n > e->cfg.max_step_tokens) { set_error("wf_seq_time_step: %d tokens", n); return WF_ERR_INVALID; }
+    std::vector<int32_t> tokens(n), want(nseq);
+    for (int i = 0; i < n; ++i) tokens[i] = (int32_t)((1103515245u * (unsigned)i + 12345u) % (unsigned)e->cfg.vocab);
+    int at_ = 0;
+    for (int i = 0; i < nseq; ++i) { at_ += counts[i]; want[i] = at_ - 1; }
+    StepView v;
+    int rc;
+    if ((rc = prepare_step(e, nseq, slots, counts, tokens.data(), nseq, want.data(), &v))) return rc;
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    for (int it = -1; it < iters; ++it) {      // one untimed pass first
+        if (it == 0) cudaEventRecord(e0, e->stream);
+        if ((rc = run_layers(e, v)) || (rc = run_head(e, v, nseq))) break;
+    }
+    cudaEventRecord(e1, e->stream);
+    const cudaError_t ce = cudaStreamSynchronize(e->stream);
+    float ms = 0.f;
+    if (!rc && ce == cudaSuccess) cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    for (int i = 0; i < nseq; ++i) e->pt.truncate(slots[i], e->h_len[slots[i]]);   // the timed tokens are not kept
+    if (rc) return rc;
+    if (cuda_check(ce, "wf_seq_time_step")) return WF_ERR_CUDA;
+    *ms_out = ms / iters;
+    return WF_OK;
+}

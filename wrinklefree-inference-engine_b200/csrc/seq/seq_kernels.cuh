@@ -1,0 +1,95 @@
+// Launchers of the sequence-model kernels; the engine (seq_engine.cu) and the per-op C ABI (seq_capi.cu) both call these.
+// dt: WF_BF16 or WF_F32 = the storage type T of weights, caches and matrix-product operands.
+#pragma once
+#include "seq_common.cuh"
+
+#define WF_F32 0
+#define WF_BF16 1
+
+namespace wf {
+namespace seq {
+
+// x[i, :] = table[tokens[i], :] as float
+int launch_embed_f32(int dt, const void* table, const int32_t* tokens, int n, int W, float* x, cudaStream_t s);
+// y = [res +] w * x / sqrt(mean_g(x^2) + eps) per row and per group of W / groups consecutive elements.  x, y, res float [n, W] with row
+// strides ldx / ldy (res shares ldy; y may alias res); rows: optional gather of the input AND residual rows.  y_t: optional T copy of y.
+int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int groups, float eps, int n, int W, const float* res, float* y,
+                         int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s);
+// causal depthwise taps over time with carried state: out_t = [identity ? in_t : 0] + sum_j w[c, j] * in_(t - taps + 1 + j), optional silu.
+// in float [n, C] (ld_in); state float [slot][taps - 1][C] (slot_stride floats between slots) = the last taps - 1 inputs of each sequence,
+// read here and rolled forward by launch_taps_state AFTER this kernel.  out: T [n, C] (out_t) and / or float (out_f).
+int launch_causal_taps(int dt, const Batch& b, const float* in, int ld_in, const void* w, int taps, int C, const float* state,
+                       size_t slot_stride, int identity, int silu, void* out_t, int ld_t, float* out_f, int ld_f, cudaStream_t s);
+int launch_taps_state(const Batch& b, const float* in, int ld_in, int taps, int C, float* state, size_t slot_stride, cudaStream_t s);
+
+// C[m, n] = sum_k A[m, k] * B[n, k]  (B stored [N, K] row-major, i.e. a Linear weight), float accumulation.
+struct GemmArgs {
+    const void* A = nullptr; int a_f32 = 0;  // A is T, or float when a_f32 (rounded to T on the tensor-core path)
+    int lda = 0;
+    const void* B = nullptr; int ldb = 0;
+    void* C = nullptr; int c_f32 = 1;        // C is float, or T
+    int ldc = 0;
+    int M = 0, N = 0, K = 0;
+    int batch = 1;                           // grid.z problems with element strides sA, sB, sC
+    long long sA = 0, sB = 0, sC = 0;
+    // grouped form (routed experts): row tile t (GEMM_BM rows) uses weight tile_group[t] (B + group * group_stride), or is skipped when < 0;
+    // a_rows (optional) gathers A rows (-1 = a zero row).  M is then the padded row count bound; m_dev (optional) the real one on the device.
+    const int32_t* tile_group = nullptr;
+    long long group_stride = 0;
+    const int32_t* a_rows = nullptr;
+};
+constexpr int GEMM_BM = 64;
+int launch_gemm(int dt, const GemmArgs& g, cudaStream_t s);
+
+// ---- latent attention ---------------------------------------------------------------------------------------------------
+struct LatentDims { int H, d, r, dv, R; float scale, rope_base; int rope_dims, window; };
+// q float [n, H * (d + r)] (ldq): unrotated parts -> qn T [n, H, d]; rotated parts -> rotary at tok_pos -> qr float [n, H, r]
+int launch_latent_q_prep(int dt, const Batch& b, const LatentDims& L, const float* q, int ldq, void* qn, float* qr, cudaStream_t s);
+// dkv float [n, R + r] (ld): first R RMS-normed with weight w (plain), last r rotated; written as T into the paged cache row of
+// (sequence, position): cache + page * page_stride + layer_off + slot_in_page * (R + r)
+struct PagedCache { void* pool; long long page_stride; long long layer_off; int page_size; const int32_t* block_table; int max_blocks; };
+int launch_latent_kv_write(int dt, const Batch& b, const LatentDims& L, const float* dkv, int ld, const void* w, float eps, const PagedCache& pc,
+                           cudaStream_t s);
+// per (token, head): softmax over positions j in (pos - window, pos] of (qa . c_j + qr . kr_j) * scale; out T [n, H, R] = sum p_j c_j.
+// qa float [n, H, R] (the query carried through the key up-projection), qr float [n, H, r].
+int launch_latent_attn(int dt, const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, cudaStream_t s);
+// y T [n, C] = x float [n, C] (ldx) * act(g float [n, C] (ldg)); act 0 = sigmoid, 1 = silu, 2 = none (a plain conversion of x)
+int launch_gate_mul(int dt, const float* x, int ldx, const float* g, int ldg, int act, int n, int C, void* y, int ldy, cudaStream_t s);
+// out T [H][C][R] = in T [H][R][C]   (per-head transpose, done once at load)
+int launch_transpose_heads(int dt, const void* in, int H, int R, int C, void* out, cudaStream_t s);
+
+// ---- gated delta rule ----------------------------------------------------------------------------------------------------
+struct DeltaDims { int H, Hk, d, dv; };
+// in place on qkv float [n, C = 2 * Hk * d + H * dv] (ld): q and k heads -> unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times d^-1/2.
+// beta[n, H] = sigmoid(b_raw), decay[n, H] = exp(-exp(A_log[h]) * softplus(a_raw + dt_bias[h]))   (a_raw, b_raw float with strides)
+int launch_delta_prep(int dt, const DeltaDims& D, int n, float* qkv, int ld, const float* a_raw, int lda, const float* b_raw, int ldb_,
+                      const void* A_log, const void* dt_bias, float* beta, float* decay, cudaStream_t s);
+// per (sequence, head): for each token in order  S = decay S;  u = beta (v - S^T k);  S += k u^T;  o = S^T q.   S float [slot][H][d][dv]
+int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int ld, const float* beta, const float* decay, float* state,
+                      size_t slot_stride, float* o, cudaStream_t s);
+// y T [n, H * dv] = o / sqrt(mean_dv(o^2) + eps) * w[dv] * silu(g float [n, H * dv] (ldg))
+int launch_delta_post(int dt, const DeltaDims& D, int n, const float* o, const void* w, float eps, const float* g, int ldg, void* y, cudaStream_t s);
+
+// ---- routed feed-forward ---------------------------------------------------------------------------------------------------
+struct RouterDims { int E, I, top, groups, keep; };   // E real experts, I identity experts (indices E .. E + I - 1)
+// z float [n, E + I] (ldz) -> ids [n, top], wts [n, top]; counts[E] += tokens per real expert (counts must be zero on entry)
+int launch_moe_route(int dt, const RouterDims& R, int n, const float* z, int ldz, const void* correction, int32_t* ids, float* wts,
+                     int32_t* counts, cudaStream_t s);
+// from counts: expert segments padded to GEMM_BM rows.  sorted_rows[P] = token of the row or -1; pair_row[n * top] = row of the pair or -1
+// (identity expert); tile_group[P / GEMM_BM] = expert of the row tile or -1.  P = row bound = round_up(n * top, BM) + E * BM.
+// scratch: 2 * E + 1 ints.
+int launch_moe_plan(const RouterDims& R, int n, const int32_t* ids, const int32_t* counts, int32_t* scratch, int32_t* sorted_rows,
+                    int32_t* pair_row, int32_t* tile_group, int P, cudaStream_t s);
+// hmid T [P, ff] = silu(gu[:, :ff]) * gu[:, ff:]   (gu float [P, 2 ff]); rows of skipped tiles are left alone
+int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s);
+// out float [n, W] = sum_k wts[t, k] * (ids[t, k] < E ? y[pair_row[t, k], :] : h[t, :])     (h T [n, W])
+int launch_moe_combine(int dt, const RouterDims& R, int n, int W, const int32_t* ids, const float* wts, const int32_t* pair_row, const float* y,
+                       const void* h, float* out, cudaStream_t s);
+
+// ---- sampling ----------------------------------------------------------------------------------------------------------------
+// next[i] = argmax (temperature <= 0) or a draw from softmax(logits / temperature) restricted to the top_k largest (0 = all) and the
+// smallest prefix whose mass reaches top_p; one uniform u[i] in [0, 1) per row.  logits float [m, V].
+int launch_sample(const float* logits, int m, int V, float temperature, int top_k, float top_p, const float* u, int32_t* next, cudaStream_t s);
+
+}  // namespace seq
+}  // namespace wf

@@ -1,0 +1,248 @@
+// Routed feed-forward: softmax router with an additive choice correction, group-limited top-k choice, identity experts, and the
+// bookkeeping that turns the chosen (token, expert) pairs into expert-contiguous, tile-padded row ranges for the grouped matrix products.
+#include "seq_kernels.cuh"
+#include <math.h>
+
+namespace wf {
+namespace seq {
+
+namespace {
+
+__device__ __forceinline__ void warp_argmax(float& v, int& idx) {   // largest value, lowest index among equals; all lanes get it
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+}
+
+// one warp per token.  shared: s[N] scores, ch[N] choice scores, gs[G] group scores
+template <typename T>
+__global__ void moe_route_kernel(RouterDims R, const float* __restrict__ z, int ldz, const T* __restrict__ correction, int32_t* __restrict__ ids,
+                                 float* __restrict__ wts, int32_t* __restrict__ counts) {
+    extern __shared__ float sm[];
+    const int N = R.E + R.I, gsz = N / R.groups;
+    float* sc = sm;
+    float* ch = sc + N;
+    float* gs = ch + N;
+    const int i = blockIdx.x, lane = threadIdx.x;
+    const float* zr = z + (size_t)i * ldz;
+    float mx = -INFINITY;
+    for (int e = lane; e < N; e += 32) mx = fmaxf(mx, zr[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < N; e += 32) { const float p = expf(zr[e] - mx); sc[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < N; e += 32) { sc[e] *= inv; ch[e] = sc[e] + to_f(correction[e]); }
+    __syncwarp();
+    // group score = largest choice score of the group; keep the best `keep` groups
+    for (int g = lane; g < R.groups; g += 32) {
+        float m = -INFINITY;
+        for (int e = g * gsz; e < (g + 1) * gsz; ++e) m = fmaxf(m, ch[e]);
+        gs[g] = m;
+    }
+    __syncwarp();
+    if (R.keep < R.groups) {
+        // the groups that are NOT among the best `keep` lose their experts: mark the winners with NaN-free sentinel +inf, then mask
+        for (int r = 0; r < R.keep; ++r) {
+            float v = -INFINITY; int gi = 0x7fffffff;
+            for (int g = lane; g < R.groups; g += 32) { const float x = gs[g]; if (x != INFINITY && (x > v || (x == v && g < gi))) { v = x; gi = g; } }
+            warp_argmax(v, gi);
+            if (lane == 0 && gi != 0x7fffffff) gs[gi] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < N; e += 32) if (gs[e / gsz] != INFINITY) ch[e] = -INFINITY;
+        __syncwarp();
+    }
+    for (int k = 0; k < R.top; ++k) {
+        float v = -INFINITY; int ei = 0x7fffffff;
+        for (int e = lane; e < N; e += 32) { const float x = ch[e]; if (!isnan(x) && (x > v || (x == v && e < ei))) { v = x; ei = e; } }
+        warp_argmax(v, ei);
+        if (ei == 0x7fffffff) ei = 0;
+        if (lane == 0) {
+            ids[(size_t)i * R.top + k] = ei;
+            wts[(size_t)i * R.top + k] = sc[ei];
+            ch[ei] = NAN;                                   // taken
+            if (ei < R.E) atomicAdd(&counts[ei], 1);
+        }
+        __syncwarp();
+    }
+}
+
+// single block.  scratch: off[E + 1], cursor[E]
+__global__ void moe_plan_kernel(RouterDims R, int n, const int32_t* __restrict__ ids, const int32_t* __restrict__ counts, int32_t* __restrict__ scratch,
+                                int32_t* __restrict__ sorted_rows, int32_t* __restrict__ pair_row, int32_t* __restrict__ tile_group, int P) {
+    int32_t* off = scratch;
+    int32_t* cursor = scratch + R.E + 1;
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < R.E; ++e) { off[e] = acc; acc += (counts[e] + GEMM_BM - 1) / GEMM_BM * GEMM_BM; cursor[e] = 0; }
+        off[R.E] = acc;
+    }
+    for (int r = threadIdx.x; r < P; r += blockDim.x) sorted_rows[r] = -1;
+    for (int t = threadIdx.x; t < P / GEMM_BM; t += blockDim.x) tile_group[t] = -1;
+    __syncthreads();
+    for (int e = 0; e < R.E; ++e)
+        for (int t = off[e] / GEMM_BM + threadIdx.x; t < off[e + 1] / GEMM_BM; t += blockDim.x) tile_group[t] = e;
+    for (int pi = threadIdx.x; pi < n * R.top; pi += blockDim.x) {
+        const int e = ids[pi];
+        if (e >= R.E) { pair_row[pi] = -1; continue; }
+        const int pos = off[e] + atomicAdd(&cursor[e], 1);
+        sorted_rows[pos] = pi / R.top;
+        pair_row[pi] = pos;
+    }
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const float* __restrict__ gu, int ff, const int32_t* __restrict__ tile_group, T* __restrict__ hmid) {
+    const int r = blockIdx.x;
+    if (tile_group && tile_group[r / GEMM_BM] < 0) return;
+    const float* row = gu + (size_t)r * 2 * ff;
+    for (int c = threadIdx.x; c < ff; c += blockDim.x) hmid[(size_t)r * ff + c] = from_f<T>(silu_f(row[c]) * row[ff + c]);
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(RouterDims R, int W, const int32_t* __restrict__ ids, const float* __restrict__ wts, const int32_t* __restrict__ pair_row,
+                                   const float* __restrict__ y, const T* __restrict__ h, float* __restrict__ out) {
+    const int i = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < R.top; ++k) {
+            const int e = ids[(size_t)i * R.top + k];
+            const float w = wts[(size_t)i * R.top + k];
+            const float v = e < R.E ? y[(size_t)pair_row[(size_t)i * R.top + k] * W + c] : to_f(h[(size_t)i * W + c]);
+            acc = fmaf(w, v, acc);
+        }
+        out[(size_t)i * W + c] = acc;
+    }
+}
+
+}  // namespace
+
+int launch_moe_route(int dt, const RouterDims& R, int n, const float* z, int ldz, const void* correction, int32_t* ids, float* wts,
+                     int32_t* counts, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    const int N = R.E + R.I;
+    if (R.groups < 1 || N % R.groups || R.keep < 1 || R.keep > R.groups || R.top < 1 || R.top > N) {
+        set_error("router: %d outputs, %d groups (keep %d), top %d", N, R.groups, R.keep, R.top);
+        return WF_ERR_INVALID;
+    }
+    const size_t smem = (size_t)(2 * N + R.groups) * sizeof(float);
+    if (smem > 48 * 1024) { set_error("router: %d outputs do not fit in shared memory", N); return WF_ERR_UNSUPPORTED; }
+    if (dt == WF_BF16) moe_route_kernel<<<n, 32, smem, s>>>(R, z, ldz, (const __nv_bfloat16*)correction, ids, wts, counts);
+    else moe_route_kernel<<<n, 32, smem, s>>>(R, z, ldz, (const float*)correction, ids, wts, counts);
+    return launch_check(cudaGetLastError(), "moe_route");
+}
+
+int launch_moe_plan(const RouterDims& R, int n, const int32_t* ids, const int32_t* counts, int32_t* scratch, int32_t* sorted_rows,
+                    int32_t* pair_row, int32_t* tile_group, int P, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (P % GEMM_BM) { set_error("moe_plan: row bound %d is not a multiple of the row tile", P); return WF_ERR_INVALID; }
+    moe_plan_kernel<<<1, 512, 0, s>>>(R, n, ids, counts, scratch, sorted_rows, pair_row, tile_group, P);
+    return launch_check(cudaGetLastError(), "moe_plan");
+}
+
+int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s) {
+    if (P <= 0) return WF_OK;
+    if (dt == WF_BF16) silu_mul_kernel<<<P, 128, 0, s>>>(gu, ff, tile_group, (__nv_bfloat16*)hmid);
+    else silu_mul_kernel<<<P, 128, 0, s>>>(gu, ff, tile_group, (float*)hmid);
+    return launch_check(cudaGetLastError(), "silu_mul");
+}
+
+int launch_moe_combine(int dt, const RouterDims& R, int n, int W, const int32_t* ids, const float* wts, const int32_t* pair_row, const float* y,
+                       const void* h, float* out, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (dt == WF_BF16) moe_combine_kernel<<<n, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const __nv_bfloat16*)h, out);
+    else moe_combine_kernel<<<n, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const float*)h, out);
+    return launch_check(cudaGetLastError(), "moe_combine");
+}
+
+// ---- sampling --------------------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int SM_THREADS = 256;
+
+__device__ float block_reduce_sum(float v, float* scratch) { return block_sum(v, scratch); }
+
+// One block per row.  Greedy: argmax, lowest index among equals.  Otherwise p = softmax(logits / temperature); the kept set is
+// {p >= tau} with tau found by bisection so that it holds at most top_k entries and is the smallest such set whose mass reaches top_p;
+// the draw walks the kept entries in index order.
+__global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restrict__ logits, int V, float temperature, int top_k, float top_p,
+                                                             const float* __restrict__ u, int32_t* __restrict__ next) {
+    __shared__ float scratch[33];
+    __shared__ float sv[SM_THREADS / 32];
+    __shared__ int si[SM_THREADS / 32];
+    __shared__ float part[SM_THREADS];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int c = tid; c < V; c += SM_THREADS) { const float x = row[c]; if (x > bv) { bv = x; bi = c; } }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    bv = sv[0]; bi = si[0];
+    for (int w = 1; w < SM_THREADS / 32; ++w) if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    if (temperature <= 0.f) { if (tid == 0) next[blockIdx.x] = bi; return; }
+    const float it = 1.f / temperature;
+    float z = 0.f;
+    for (int c = tid; c < V; c += SM_THREADS) z += expf((row[c] - bv) * it);
+    z = block_reduce_sum(z, scratch);
+    // bisection on tau in (0, 1]: unnormalised weight w_c = exp((x_c - max) / T) in (0, 1]
+    float lo = 0.f, hi = 1.f;                        // keep {w >= tau}; tau = lo keeps everything
+    const bool limit = (top_k > 0 && top_k < V) || (top_p > 0.f && top_p < 1.f);
+    if (limit) {
+        for (int it_ = 0; it_ < 30; ++it_) {
+            const float tau = 0.5f * (lo + hi);
+            float cnt = 0.f, mass = 0.f;
+            for (int c = tid; c < V; c += SM_THREADS) { const float w = expf((row[c] - bv) * it); if (w >= tau) { cnt += 1.f; mass += w; } }
+            cnt = block_reduce_sum(cnt, scratch);
+            mass = block_reduce_sum(mass, scratch);
+            const bool k_ok = !(top_k > 0 && top_k < V) || cnt <= (float)top_k;
+            const bool p_reached = !(top_p > 0.f && top_p < 1.f) || mass >= top_p * z;
+            // raise tau while the set is still too large for top_k, or still reaches top_p (a smaller set may do)
+            if (!k_ok || (p_reached && cnt > 1.f)) lo = tau; else hi = tau;
+        }
+    }
+    const float tau = limit ? lo : 0.f;
+    // kept mass per thread over a contiguous chunk, then the draw
+    const int chunk = (V + SM_THREADS - 1) / SM_THREADS;
+    const int c0 = tid * chunk, c1 = c0 + chunk < V ? c0 + chunk : V;
+    float mine = 0.f;
+    for (int c = c0; c < c1; ++c) { const float w = expf((row[c] - bv) * it); if (w >= tau) mine += w; }
+    part[tid] = mine;
+    __syncthreads();
+    if (tid == 0) {
+        float total = 0.f;
+        for (int t = 0; t < SM_THREADS; ++t) total += part[t];
+        float target = u[blockIdx.x] * total, run = 0.f;
+        int pick = bi, t = 0;
+        for (; t < SM_THREADS; ++t) { if (run + part[t] > target) break; run += part[t]; }
+        if (t < SM_THREADS) {
+            const int a0 = t * chunk, a1 = a0 + chunk < V ? a0 + chunk : V;
+            for (int c = a0; c < a1; ++c) {
+                const float w = expf((row[c] - bv) * it);
+                if (w >= tau) { run += w; if (run > target) { pick = c; break; } }
+            }
+        }
+        next[blockIdx.x] = pick;
+    }
+}
+
+}  // namespace
+
+int launch_sample(const float* logits, int m, int V, float temperature, int top_k, float top_p, const float* u, int32_t* next, cudaStream_t s) {
+    if (m <= 0) return WF_OK;
+    if (temperature > 0.f && !u) { set_error("sample: uniforms required when temperature > 0"); return WF_ERR_INVALID; }
+    sample_kernel<<<m, SM_THREADS, 0, s>>>(logits, V, temperature, top_k, top_p, u, next);
+    return launch_check(cudaGetLastError(), "sample");
+}
+
+}  // namespace seq
+}  // namespace wf

@@ -1,0 +1,140 @@
+// Row-wise kernels of the sequence models: embedding gather, grouped RMS norm (+ residual add), causal depthwise taps with carried state.
+#include "seq_kernels.cuh"
+
+namespace wf {
+namespace seq {
+
+template <typename T>
+__global__ void embed_f32_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens, int W, float* __restrict__ x) {
+    const int i = blockIdx.x;
+    const T* row = table + (size_t)tokens[i] * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) x[(size_t)i * W + c] = to_f(row[c]);
+}
+
+int launch_embed_f32(int dt, const void* table, const int32_t* tokens, int n, int W, float* x, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (dt == WF_BF16) embed_f32_kernel<<<n, 256, 0, s>>>((const __nv_bfloat16*)table, tokens, W, x);
+    else embed_f32_kernel<<<n, 256, 0, s>>>((const float*)table, tokens, W, x);
+    return launch_check(cudaGetLastError(), "embed_f32");
+}
+
+// one block per (row, group)
+template <typename T>
+__global__ void group_rmsnorm_kernel(const float* __restrict__ x, int ldx, const T* __restrict__ w, int gw, float eps, const float* res,
+                                     float* y, int ldy, T* __restrict__ y_t, int ldt, const int32_t* __restrict__ rows) {
+    __shared__ float scratch[33];
+    const int i = blockIdx.x, g = blockIdx.y;
+    const int src = rows ? rows[i] : i;
+    const float* xr = x + (size_t)src * ldx + (size_t)g * gw;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < gw; c += blockDim.x) { const float v = xr[c]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)gw + eps);
+    for (int c = threadIdx.x; c < gw; c += blockDim.x) {
+        float v = xr[c] * inv * to_f(w[g * gw + c]);
+        if (res) v += res[(size_t)src * ldy + g * gw + c];
+        if (y) y[(size_t)i * ldy + g * gw + c] = v;
+        if (y_t) y_t[(size_t)i * ldt + g * gw + c] = from_f<T>(v);
+    }
+}
+
+int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int groups, float eps, int n, int W, const float* res, float* y,
+                         int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (groups <= 0 || W % groups) { set_error("group_rmsnorm: width %d not divisible into %d groups", W, groups); return WF_ERR_INVALID; }
+    if (res && rows && y == res) { set_error("group_rmsnorm: gathered rows cannot be added in place"); return WF_ERR_INVALID; }
+    const int gw = W / groups;
+    const int threads = gw >= 1024 ? 256 : (gw >= 256 ? 128 : 64);
+    dim3 grid(n, groups);
+    if (dt == WF_BF16) group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const __nv_bfloat16*)w, gw, eps, res, y, ldy, (__nv_bfloat16*)y_t, ldt, rows);
+    else group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const float*)w, gw, eps, res, y, ldy, (float*)y_t, ldt, rows);
+    return launch_check(cudaGetLastError(), "group_rmsnorm");
+}
+
+// thread per (token, channel)
+template <typename T>
+__global__ void causal_taps_kernel(Batch b, const float* __restrict__ in, int ld_in, const T* __restrict__ w, int taps, int C,
+                                   const float* __restrict__ state, size_t slot_stride, int identity, int silu, T* __restrict__ out_t, int ld_t,
+                                   float* __restrict__ out_f, int ld_f) {
+    const int i = blockIdx.x;
+    const int sq = b.tok_seq[i];
+    const int li = i - b.seq_start[sq];                    // index inside this step's portion
+    const float* st = state + (size_t)b.seq_slot[sq] * slot_stride;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float acc = identity ? in[(size_t)i * ld_in + c] : 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = li - (taps - 1) + j;           // portion-relative index of the tap's input
+            const float v = src >= 0 ? in[(size_t)(i - li + src) * ld_in + c] : st[(size_t)(src + taps - 1) * C + c];
+            acc = fmaf(to_f(w[(size_t)c * taps + j]), v, acc);
+        }
+        if (silu) acc = silu_f(acc);
+        if (out_t) out_t[(size_t)i * ld_t + c] = from_f<T>(acc);
+        if (out_f) out_f[(size_t)i * ld_f + c] = acc;
+    }
+}
+
+int launch_causal_taps(int dt, const Batch& b, const float* in, int ld_in, const void* w, int taps, int C, const float* state,
+                       size_t slot_stride, int identity, int silu, void* out_t, int ld_t, float* out_f, int ld_f, cudaStream_t s) {
+    if (b.n <= 0) return WF_OK;
+    if (taps < 1) { set_error("causal_taps: taps %d", taps); return WF_ERR_INVALID; }
+    dim3 grid(b.n, (C + 255) / 256 > 8 ? 8 : (C + 255) / 256);
+    if (dt == WF_BF16) causal_taps_kernel<<<grid, 256, 0, s>>>(b, in, ld_in, (const __nv_bfloat16*)w, taps, C, state, slot_stride, identity, silu, (__nv_bfloat16*)out_t, ld_t, out_f, ld_f);
+    else causal_taps_kernel<<<grid, 256, 0, s>>>(b, in, ld_in, (const float*)w, taps, C, state, slot_stride, identity, silu, (float*)out_t, ld_t, out_f, ld_f);
+    return launch_check(cudaGetLastError(), "causal_taps");
+}
+
+// thread per (sequence, channel): state[k] <- input at portion index len - (taps - 1) + k, taken from the old state when that is negative.
+// Ascending k is safe in place: entry k reads old entry len + k > k.
+__global__ void taps_state_kernel(Batch b, const float* __restrict__ in, int ld_in, int taps, int C, float* __restrict__ state, size_t slot_stride) {
+    const int sq = blockIdx.x;
+    const int len = b.seq_len[sq], start = b.seq_start[sq];
+    float* st = state + (size_t)b.seq_slot[sq] * slot_stride;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        for (int k = 0; k < taps - 1; ++k) {
+            const int src = len - (taps - 1) + k;
+            st[(size_t)k * C + c] = src >= 0 ? in[(size_t)(start + src) * ld_in + c] : st[(size_t)(src + taps - 1) * C + c];
+        }
+    }
+}
+
+int launch_taps_state(const Batch& b, const float* in, int ld_in, int taps, int C, float* state, size_t slot_stride, cudaStream_t s) {
+    if (b.nseq <= 0 || taps <= 1) return WF_OK;
+    dim3 grid(b.nseq, (C + 255) / 256 > 8 ? 8 : (C + 255) / 256);
+    taps_state_kernel<<<grid, 256, 0, s>>>(b, in, ld_in, taps, C, state, slot_stride);
+    return launch_check(cudaGetLastError(), "taps_state");
+}
+
+template <typename T>
+__global__ void gate_mul_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ g, int ldg, int act, int C, T* __restrict__ y, int ldy) {
+    const int i = blockIdx.x;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float z = g[(size_t)i * ldg + c];
+        y[(size_t)i * ldy + c] = from_f<T>(x[(size_t)i * ldx + c] * (act == 2 ? 1.f : (act ? silu_f(z) : sigmoid_f(z))));
+    }
+}
+
+int launch_gate_mul(int dt, const float* x, int ldx, const float* g, int ldg, int act, int n, int C, void* y, int ldy, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (dt == WF_BF16) gate_mul_kernel<<<n, 256, 0, s>>>(x, ldx, g, ldg, act, C, (__nv_bfloat16*)y, ldy);
+    else gate_mul_kernel<<<n, 256, 0, s>>>(x, ldx, g, ldg, act, C, (float*)y, ldy);
+    return launch_check(cudaGetLastError(), "gate_mul");
+}
+
+template <typename T>
+__global__ void transpose_heads_kernel(const T* __restrict__ in, int R, int C, T* __restrict__ out) {
+    const size_t h = blockIdx.y;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < R * C; idx += gridDim.x * blockDim.x) {
+        const int r = idx / C, c = idx % C;
+        out[h * R * C + (size_t)c * R + r] = in[h * R * C + idx];
+    }
+}
+
+int launch_transpose_heads(int dt, const void* in, int H, int R, int C, void* out, cudaStream_t s) {
+    dim3 grid((R * C + 255) / 256 > 1024 ? 1024 : (R * C + 255) / 256, H);
+    if (dt == WF_BF16) transpose_heads_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, R, C, (__nv_bfloat16*)out);
+    else transpose_heads_kernel<<<grid, 256, 0, s>>>((const float*)in, R, C, (float*)out);
+    return launch_check(cudaGetLastError(), "transpose_heads");
+}
+
+}  // namespace seq
+}  // namespace wf

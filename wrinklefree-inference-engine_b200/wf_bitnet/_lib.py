@@ -109,6 +109,94 @@ SYMBOLS = {
 
 _lib = None
 
+# ---- libwf_seq.so (include/wf_seq.h): the engine for layer-stack sequence models ------------------------------------------------
+SEQ_LIB_PATH = Path(os.environ.get("WF_SEQ_LIB", _PKG_ROOT / "libwf_seq.so"))
+WF_SEQ_F32, WF_SEQ_BF16 = 0, 1
+WF_SEQ_LATENT_ATTENTION, WF_SEQ_DELTA = 0, 1
+
+
+class SeqLayer(C.Structure):
+    _fields_ = [
+        ("type", C.c_int), ("heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int),
+        ("rot_dim", C.c_int), ("kv_rank", C.c_int), ("window", C.c_int), ("rope_dims", C.c_int),
+        ("scale", C.c_float), ("rope_base", C.c_float),
+        ("kv_heads", C.c_int), ("conv", C.c_int),
+        ("has_ff", C.c_int), ("experts", C.c_int), ("identity", C.c_int), ("top", C.c_int), ("groups", C.c_int), ("keep", C.c_int),
+        ("ff", C.c_int),
+    ]
+
+
+class SeqConfig(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int), ("vocab", C.c_int), ("width", C.c_int), ("n_layers", C.c_int), ("eps", C.c_float),
+        ("norm_groups", C.c_int), ("canon_taps", C.c_int), ("page_size", C.c_int), ("max_pages", C.c_int), ("slots", C.c_int),
+        ("max_step_tokens", C.c_int),
+    ]
+
+
+_ip, _fp = C.POINTER(C.c_int32), C.POINTER(C.c_float)
+SEQ_SYMBOLS = {
+    "wf_last_error": (C.c_char_p, []),
+    "wf_seq_available": (_i, []),
+    "wf_seq_create": (_i, [C.POINTER(SeqConfig), C.POINTER(SeqLayer), C.POINTER(_vp)]),
+    "wf_seq_destroy": (None, [_vp]),
+    "wf_seq_device_bytes": (_sz, [_vp]),
+    "wf_seq_set_tensor": (_i, [_vp, C.c_char_p, _vp, _sz, _i]),
+    "wf_seq_tensor_count": (_i, [_vp]),
+    "wf_seq_tensor_name": (C.c_char_p, [_vp, _i, C.POINTER(_sz), C.POINTER(_i)]),
+    "wf_seq_finalize": (_i, [_vp]),
+    "wf_seq_admit": (_i, [_vp, C.POINTER(_i)]),
+    "wf_seq_release": (_i, [_vp, _i]),
+    "wf_seq_length": (_i, [_vp, _i]),
+    "wf_seq_free_pages": (_i, [_vp]),
+    "wf_seq_free_slots": (_i, [_vp]),
+    "wf_seq_step": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp]),
+    "wf_seq_sample": (_i, [_vp, _i, _f, _i, _f, _vp, _vp]),
+    "wf_seq_logits_device": (_vp, [_vp]),
+    "wf_seq_launches_last_step": (_i, [_vp]),
+    "wf_seq_set_layer_tap": (_i, [_vp, _vp]),
+    "wf_seq_run_part": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "wf_seq_time_step": (_i, [_vp, _i, _vp, _vp, _i, _fp]),
+}
+_seq_lib = None
+
+
+def build_seq_lib() -> None:
+    """Compile libwf_seq.so in-tree (make target `seq`: the sequence-model sources only)."""
+    import subprocess
+    env = dict(os.environ)
+    env.pop("CC", None)
+    env.pop("CXX", None)
+    subprocess.run(["make", "-C", str(_PKG_ROOT / "csrc"), "seq", "-j8"], check=True, env=env, stdout=subprocess.DEVNULL)
+
+
+def seq_lib(build: bool = False) -> C.CDLL:
+    """Load libwf_seq.so and bind every symbol of include/wf_seq.h.  build=True compiles it first when it is absent."""
+    global _seq_lib
+    if _seq_lib is None:
+        if not SEQ_LIB_PATH.exists():
+            if not build:
+                raise WfError(f"{SEQ_LIB_PATH} not found: build it with `make -C {_PKG_ROOT / 'csrc'} seq`. There is no CPU fallback.")
+            build_seq_lib()
+        L = C.CDLL(str(SEQ_LIB_PATH))
+        for name, (res, args) in SEQ_SYMBOLS.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _seq_lib = L
+    return _seq_lib
+
+
+def seq_check(rc: int) -> None:
+    if rc == WF_OK:
+        return
+    msg = seq_lib().wf_last_error().decode("utf-8", "replace")
+    if rc == WF_ERR_INVALID:
+        raise ValueError(msg)
+    if rc == WF_ERR_UNSUPPORTED:
+        raise NotImplementedError(msg)
+    raise WfError(msg)
+
 
 def lib() -> C.CDLL:
     """Load libwf_bitnet.so and bind every declared symbol.  Raises if the library is absent."""
