@@ -1,7 +1,10 @@
 #!/usr/bin/env python
 """bench.py — decode throughput of the BitNet-2B-4T-shaped hot path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload bs64|bs1]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload bs64|bs1|hybrid]
+
+--workload hybrid (1 GPU) measures the layer-stack sequence engine (latent attention / gated delta rule / routed feed-forward) instead:
+prefill and decode tok/s at two layer sizes with random weights, per launch-group times, and the BitNet engine at equal size beside it.
 
 A "step" is one decode step (one new token for every sequence of the batch) of the
 BitNet-2B-4T-shaped model: 30 layers x (rmsnorm+int8 quant, fused q|k|v ternary linear, RoPE + paged KV
@@ -768,17 +771,152 @@ def run_gpu(args):
     return 0
 
 
+
+# ---------------------------------------------------------------------------------------------------------------------------------
+# --workload hybrid: the layer-stack sequence engine (Karusun design: latent attention / gated delta rule mixers + routed feed-forward)
+# at sizes that resemble real layers, random weights, beside the BitNet engine at equal width / heads / active feed-forward size.
+HYBRID_SIZES = {
+    # name: width, heads, latent (dim, rot_dim, vdim, kv_rank, window), delta (kv_heads, dim, vdim), experts, identity, top, groups, keep, ff, vocab, layers
+    "w1024": dict(width=1024, heads=8, d=64, r=32, dv=64, R=256, window=1024, dk_heads=4, dd=64, ddv=128, experts=30, identity=2, top=6, groups=4, keep=2,
+                  ff=384, vocab=32768, layers=4),
+    "w2560": dict(width=2560, heads=20, d=96, r=32, dv=128, R=512, window=4096, dk_heads=10, dd=128, ddv=128, experts=30, identity=2, top=6, groups=4, keep=2,
+                  ff=1152, vocab=128256, layers=4),
+}
+
+
+def hybrid_config(z):
+    lat = {"type": "latent_attention", "mixer": {"heads": z["heads"], "dim": z["d"], "rot_dim": z["r"], "vdim": z["dv"], "kv_rank": z["R"],
+                                                  "mask": {"size": z["window"]}, "rot": {"base": 10000.0, "dims": z["r"]}, "scale": (z["d"] + z["r"]) ** -0.5}}
+    dl = {"type": "delta", "mixer": {"heads": z["heads"], "kv_heads": z["dk_heads"], "dim": z["dd"], "vdim": z["ddv"], "conv": 4}}
+    ff = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"],
+                                                                "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    layers = [dict(dl if (i % 4) == 3 else lat, mlp=ff) for i in range(z["layers"])]
+    return {"architecture": "Karusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5, "groups": 4}, "canon": {"taps": 4}, "layers": layers}
+
+
+def hybrid_model(cfg, max_tokens, slots, max_step_tokens):
+    from wf_bitnet import registry
+    m = registry.resolve(cfg)(cfg, dtype="bfloat16", max_tokens=max_tokens, slots=slots, page_size=16, max_step_tokens=max_step_tokens)
+    rng = np.random.default_rng(0)
+    base = torch.from_numpy(rng.standard_normal(1 << 22).astype(np.float32)).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    for name, count, _ in m.engine.expected_tensors():
+        # random values of the scale a trained layer has (~ 1 / sqrt(fan-in)); norm weights near 1
+        if name.endswith(("norm1", "norm2", "norm1b", "norm2b", "final.norm", ".norm")):
+            a = np.full(count, 0x3F80, dtype=np.uint16)
+        else:
+            vals = torch.from_numpy(base.view(np.int16)).view(torch.bfloat16).float().numpy()
+            scale = 0.02 if count > 4096 else 0.5
+            a = torch.from_numpy(np.resize(vals, count) * scale).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+        m.engine.set_tensor(name, a)
+    m.engine.finalize()
+    return m
+
+
+def hybrid_layer_bytes(z):
+    """weight bytes one decoded token must read per layer kind (bf16): fused projections + up-projections + output + router + chosen experts"""
+    W, H = z["width"], z["heads"]
+    lat = (H * (z["d"] + z["r"]) + z["R"] + z["r"] + H * z["dv"]) * W + H * z["d"] * z["R"] + H * z["dv"] * z["R"] + W * H * z["dv"]
+    dl = (2 * z["dk_heads"] * z["dd"] + 2 * H * z["ddv"] + 2 * H) * W + W * H * z["ddv"]
+    ffb = (z["experts"] + z["identity"]) * W + 3 * z["ff"] * W          # per chosen real expert
+    return {"latent": 2 * lat, "delta": 2 * dl, "router": 2 * (z["experts"] + z["identity"]) * W, "expert": 2 * 3 * z["ff"] * W, "ff_nominal": 2 * ffb}
+
+
+def run_hybrid(args):
+    from wf_bitnet import _lib
+    from wf_bitnet.engine import Engine, EngineConfig
+    torch.cuda.set_device(0)
+    _lib.require_gpu()
+    K, W_ = max(2, args.steps), max(3, args.warmup)
+    peak, peak_src = measured_peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
+    out = {}
+    launches = 0
+    for name, z in HYBRID_SIZES.items():
+        if args.hybrid_size and name != args.hybrid_size:
+            continue
+        cfg = hybrid_config(z)
+        res = {"layers": z["layers"], "layer_kinds": [L["type"] for L in cfg["layers"]]}
+        prompt = 2048
+        decode_points = [(1, 512), (8, 2048), (64, 4096)] if name == "w2560" else [(1, 512), (8, 1024), (64, 1024)]
+        max_b = max(b for b, _ in decode_points)
+        tokens_cap = max(max(b * (c + 16) for b, c in decode_points), prompt + 16)
+        m = hybrid_model(cfg, tokens_cap, max_b, prompt)
+        slots = [m.admit() for _ in range(max_b)]
+        # prefill: one prompt of 2048 tokens from an empty cache
+        ms = m.engine.time_step(slots[:1], [prompt], iters=K)
+        res["prefill"] = {"tokens": prompt, "ms": round(ms, 3), "tok_s": round(prompt / ms * 1e3, 1)}
+        res["prefill_profile_ms"] = {k: round(v[0], 4) for k, v in m.engine.profile_step(slots[:1], [prompt], iters=2).items()}
+        launches += m.engine.launches_last_step()
+        res["decode"] = {}
+        for b, ctx in decode_points:
+            for s_ in slots[:b]:
+                m.engine.set_length(s_, ctx)
+            ms = m.engine.time_step(slots[:b], [1] * b, iters=max(K, 10))
+            res["decode"][f"bs{b}_ctx{ctx}"] = {"ms": round(ms, 4), "tok_s": round(b / ms * 1e3, 1)}
+            if b in (1, 64):
+                res[f"decode_profile_ms_bs{b}"] = {k: round(v[0], 4) for k, v in m.engine.profile_step(slots[:b], [1] * b, iters=3).items()}
+        res["weight_bytes_per_token"] = hybrid_layer_bytes(z)
+        res["device_bytes"] = m.engine.device_bytes()
+        m.close()
+        # the closest existing model at equal size: the BitNet engine (GQA attention + dense ternary feed-forward), decode only —
+        # it has no prompt path: prompts are read token by token at the batch-1 decode rate
+        ffn = ((z["top"] * z["ff"] + 127) // 128) * 128
+        bres = {}
+        for b, ctx in decode_points:
+            ecfg = EngineConfig(hidden=z["width"], layers=z["layers"], heads=z["heads"], kv_heads=max(1, z["heads"] // 4), head_dim=128, ffn=ffn,
+                                vocab=z["vocab"], max_seq=ctx + 64, page_size=16, max_batch=b)
+            eng = Engine(ecfg)
+            eng.init_synthetic(7)
+            for slot in range(b):
+                eng.set_context(slot, ctx, fill_random=True)
+            toks = np.zeros(b, dtype=np.int32)
+            eng.decode(toks)
+            ext = torch.cuda.ExternalStream(eng.stream)
+            for _ in range(W_):
+                eng.decode_device(b)
+            eng.sync()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(ext)
+            for _ in range(max(K, 10)):
+                eng.decode_device(b)
+            e1.record(ext)
+            e1.synchronize()
+            ms = e0.elapsed_time(e1) / max(K, 10)
+            bres[f"bs{b}_ctx{ctx}"] = {"ms": round(ms, 4), "tok_s": round(b / ms * 1e3, 1)}
+            if b == 1:
+                bres["prompt_tok_s_token_by_token"] = round(1e3 / ms, 1)
+            eng.close()
+        res["bitnet_equal_size_decode"] = bres
+        out[name] = res
+    clocks = sampler.stop()
+    head = out.get("w2560") or next(iter(out.values()))
+    top = sorted(head["decode"].items())[-1]
+    emit({"metric": "prefill / decode tok/s of the hybrid sequence engine (Karusun design) beside the BitNet engine at equal size", "workload": "hybrid",
+          "value": top[1]["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W_, "higher_is_better": True, "dtype": "bf16",
+          "data": "synthetic (random weights; decode contexts are zero-filled cache pages)", "vs_baseline": None,
+          "config": {"model": "Karusun-shaped, " + ", ".join(out), "point": top[0], "l2": "weights per step exceed L2 (126 MB) at w2560; w1024 is L2-resident"},
+          "hbm_peak_gbs": peak, "peak_source": peak_src, "sizes": out, "clocks": clocks, "gpu_launches": launches})
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="bs64", choices=["bs64", "bs1"] + sorted(TP_WORKLOADS))
+    ap.add_argument("--workload", default="bs64", choices=["bs64", "bs1", "hybrid"] + sorted(TP_WORKLOADS))
+    ap.add_argument("--hybrid-size", default="", help="--workload hybrid: run only this size (w1024 | w2560)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-aux", action="store_true", help="skip the batch-1 aux measurement")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel suite (aux.tp)")
     args = ap.parse_args()
+    if args.workload == "hybrid":
+        if args.impl == "reference":
+            emit({"impl": "reference", "unavailable": "the reference has no model of this design; its arm is defined for the 2B workloads only"})
+            return 0
+        return run_hybrid(args)
     if args.workload in TP_WORKLOADS:
         if args.impl == "reference":
             emit({"impl": "reference", "unavailable": "the reference arm is defined for the 2B workloads (bs64 / bs1) only"})

@@ -9,6 +9,7 @@
 //   -> sub-norm+quant -> down linear (+residual).
 #include "kernels.cuh"
 #include "fused_common.cuh"
+#include "pager.h"
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
@@ -56,10 +57,8 @@ struct wf_engine {
     float* kv_scales = nullptr;      // int8 KV: scale region [page][layer][K|V][head][slot]
     int max_blocks = 0;
     int32_t* d_block_table = nullptr;
-    std::vector<int32_t> h_block_table;
-    std::vector<int32_t> free_pages;
+    PageTable pt;                    // free list + one block-table row per batch slot (pager.h, shared with the sequence-model engine)
     std::vector<int32_t> h_pos;
-    bool table_dirty = true;
     int32_t *d_pos = nullptr, *d_len = nullptr, *d_tok = nullptr, *d_next = nullptr;
     int32_t *h_tok_pinned = nullptr, *h_next_pinned = nullptr, *h_pos_pinned = nullptr;
     // activations
@@ -505,21 +504,15 @@ int prepare_pages(wf_engine* e, int B) {
     for (int b = 0; b < B; ++b) {
         const int pos = e->h_pos[b];
         if (pos >= e->cfg.max_seq) { set_error("sequence %d reached max_seq %d", b, e->cfg.max_seq); return WF_ERR_INVALID; }
-        const int blk = pos / ps;
-        if (e->h_block_table[(size_t)b * e->max_blocks + blk] < 0) {
-            if (e->free_pages.empty()) { set_error("KV pool exhausted (%d pages)", e->cfg.max_pages); return WF_ERR_INVALID; }
-            e->h_block_table[(size_t)b * e->max_blocks + blk] = e->free_pages.back();
-            e->free_pages.pop_back();
-            e->table_dirty = true;
-        }
+        if (!e->pt.ensure(b, pos + 1)) { set_error("KV pool exhausted (%d pages)", e->cfg.max_pages); return WF_ERR_INVALID; }
     }
-    if (e->table_dirty) {
+    if (e->pt.dirty) {
         // unused entries point at page 0 so that a stale lookup can never leave the pool
-        std::vector<int32_t> tmp(e->h_block_table);
+        std::vector<int32_t> tmp(e->pt.table);
         for (auto& v : tmp) if (v < 0) v = 0;
         if (cuda_check(cudaMemcpyAsync(e->d_block_table, tmp.data(), tmp.size() * 4, cudaMemcpyHostToDevice, e->stream), "block table H2D")) return WF_ERR_CUDA;
         if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) return WF_ERR_CUDA;   // tmp is pageable
-        e->table_dirty = false;
+        e->pt.dirty = false;
     }
     return WF_OK;
 }
@@ -784,7 +777,7 @@ extern "C" int wf_engine_create(const wf_model_config* cfg, wf_engine** out) {
         if ((rc = dalloc(e, &e->trace, (size_t)32 * (5 * c.layers + 8)))) return fail(rc);
         cudaMemset(e->trace, 0, (size_t)32 * (5 * c.layers + 8) * 8);
     }
-    e->h_block_table.assign((size_t)B * e->max_blocks, -1);
+    e->pt.init(c.max_pages, c.page_size, B, e->max_blocks);
     e->h_pos.assign(B, 0);
     wf_engine_reset(e);
     *out = e;
@@ -944,11 +937,8 @@ extern "C" int wf_engine_init_synthetic(wf_engine* e, uint64_t seed) {
 extern "C" int wf_engine_reset(wf_engine* e) {
     if (!e) return WF_ERR_INVALID;
     const int B = e->cfg.max_batch;
-    e->free_pages.clear();
-    for (int p = e->cfg.max_pages - 1; p >= 0; --p) e->free_pages.push_back(p);   // pop_back hands out 0,1,2,... like the reference free list
-    std::fill(e->h_block_table.begin(), e->h_block_table.end(), -1);
+    e->pt.reset();   // pages are handed out 0,1,2,... like the reference free list
     std::fill(e->h_pos.begin(), e->h_pos.end(), 0);
-    e->table_dirty = true;
     if (cuda_check(cudaMemsetAsync(e->d_pos, 0, B * 4, e->stream), "reset")) return WF_ERR_CUDA;
     std::vector<int32_t> ones(B, 1);
     if (cuda_check(cudaMemcpyAsync(e->d_len, ones.data(), B * 4, cudaMemcpyHostToDevice, e->stream), "reset")) return WF_ERR_CUDA;
@@ -959,19 +949,9 @@ extern "C" int wf_engine_set_context(wf_engine* e, int slot, int len, int fill_r
     if (!e || slot < 0 || slot >= e->cfg.max_batch || len < 0 || len >= e->cfg.max_seq) { set_error("wf_engine_set_context: bad slot/len"); return WF_ERR_INVALID; }
     const int ps = e->cfg.page_size;
     // release pages beyond the new length, allocate up to it
-    for (int blk = 0; blk < e->max_blocks; ++blk) {
-        int32_t& ent = e->h_block_table[(size_t)slot * e->max_blocks + blk];
-        const bool need = blk * ps < len;
-        if (need && ent < 0) {
-            if (e->free_pages.empty()) { set_error("KV pool exhausted"); return WF_ERR_INVALID; }
-            ent = e->free_pages.back();
-            e->free_pages.pop_back();
-        } else if (!need && ent >= 0) {
-            e->free_pages.push_back(ent);
-            ent = -1;
-        }
-    }
-    e->table_dirty = true;
+    e->pt.truncate(slot, len);
+    if (!e->pt.ensure(slot, len)) { set_error("KV pool exhausted"); return WF_ERR_INVALID; }
+    e->pt.dirty = true;
     e->h_pos[slot] = len;
     // on the engine stream (it is cudaStreamNonBlocking: a default-stream copy could race an in-flight asynchronous step, whose
     // advance kernel updates the same words)
@@ -983,7 +963,7 @@ extern "C" int wf_engine_set_context(wf_engine* e, int slot, int len, int fill_r
         // a page is one contiguous run of layers*2*Hkv*page_size*D elements
         const size_t page_elems = (size_t)e->cfg.layers * 2 * e->Hkv * ps * e->D;
         for (int blk = 0; blk * ps < len; ++blk) {
-            const int32_t page = e->h_block_table[(size_t)slot * e->max_blocks + blk];
+            const int32_t page = e->pt.row(slot)[blk];
             int rc;
             if (e->kv_scales) {   // random int8 codes (the bytes of random bf16 values) and scales of N(1, 0.1)/42 so that values are O(1)
                 rc = launch_fill_bf16(reinterpret_cast<unsigned char*>(e->pool) + (size_t)page * page_elems, page_elems / 2, 0xC0FFEEull + (uint64_t)page, 0.0f, 1.0f, e->stream);

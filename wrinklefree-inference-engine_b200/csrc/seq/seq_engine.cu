@@ -69,15 +69,19 @@ struct wf_seq_engine {
     // workspace
     float *x = nullptr, *hn = nullptr, *y = nullptr, *proj = nullptr, *qr = nullptr, *qa = nullptr, *ov = nullptr, *qkvc = nullptr, *beta = nullptr,
           *decay = nullptr, *od = nullptr, *z = nullptr, *wts = nullptr, *gu = nullptr, *yexp = nullptr;
-    void *h_t = nullptr, *qn = nullptr, *olat = nullptr, *og = nullptr, *hmid = nullptr, *xn = nullptr;
+    void *hperm = nullptr, *h_t = nullptr, *qn = nullptr, *olat = nullptr, *og = nullptr, *hmid = nullptr, *xn = nullptr;
     int32_t *ids = nullptr, *counts = nullptr, *plan_scratch = nullptr, *sorted_rows = nullptr, *pair_row = nullptr, *tile_group = nullptr;
     int P = 0;                        // padded expert-row bound
+    int pair_path_max = 64;           // up to this many (token, expert) pairs the experts run as per-pair weight streams (WF_SEQ_PAIR_MAX)
     float* logits = nullptr;
     size_t logits_rows = 0;
     float* d_uniform = nullptr;
     int32_t* d_next = nullptr;
     size_t sample_rows = 0;
     float* layer_tap = nullptr;
+    // per-kernel-kind timing (wf_seq_profile_step): an event after every launch group; the time since the previous event goes to its label
+    bool prof = false;
+    std::vector<std::pair<const char*, cudaEvent_t>> marks;
     int launches = 0;
     size_t dev_bytes = 0;
     std::vector<void*> allocs;
@@ -131,6 +135,14 @@ int validate(const wf_seq_config& c, const wf_seq_layer* L) {
         }
     }
     return WF_OK;
+}
+
+void mark(wf_seq_engine* e, const char* label) {
+    if (!e->prof) return;
+    cudaEvent_t ev;
+    cudaEventCreate(&ev);
+    cudaEventRecord(ev, e->stream);
+    e->marks.push_back({label, ev});
 }
 
 struct StepView {
@@ -211,21 +223,29 @@ int run_latent(wf_seq_engine* e, LayerState& L, const Batch& b) {
     LatentDims D{H, c.dim, c.rot_dim, c.vdim, c.kv_rank, c.scale, c.rope_base, c.rope_dims, c.window};
     PagedCache pc{e->pool, e->page_stride, L.cache_off, e->cfg.page_size, e->d_block_table, e->pt.max_blocks};
     if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q | dkv | g]
+    mark(e, "latent.proj_gemm");
     if ((rc = launch_latent_q_prep(e->dt, b, D, e->proj, L.np, e->qn, e->qr, s))) return rc;
     if ((rc = launch_latent_kv_write(e->dt, b, D, e->proj + nq, L.np, L.dkv_norm, e->cfg.eps, pc, s))) return rc;
+    mark(e, "latent.q_prep+kv_write");
     {   // qa[i, h, :] = W_uk[h]^T qn[i, h, :]
         GemmArgs g = lin(e->qn, 0, H * c.dim, L.ukT, c.dim, e->qa, 1, H * c.kv_rank, n, c.kv_rank, c.dim);
         g.batch = H; g.sA = c.dim; g.sB = (long long)c.kv_rank * c.dim; g.sC = c.kv_rank;
         if ((rc = launch_gemm(e->dt, g, s))) return rc;
+        mark(e, "latent.absorb_gemm");
     }
     if ((rc = launch_latent_attn(e->dt, b, D, e->qa, e->qr, pc, e->olat, s))) return rc;
+    mark(e, "latent.attention");
     {   // ov[i, h, :] = W_uv[h] olat[i, h, :]
         GemmArgs g = lin(e->olat, 0, H * c.kv_rank, L.uv, c.kv_rank, e->ov, 1, nv, n, c.vdim, c.kv_rank);
         g.batch = H; g.sA = c.kv_rank; g.sB = (long long)c.vdim * c.kv_rank; g.sC = c.vdim;
         if ((rc = launch_gemm(e->dt, g, s))) return rc;
+        mark(e, "latent.value_up_gemm");
     }
     if ((rc = launch_gate_mul(e->dt, e->ov, nv, e->proj + nq + nkv, L.np, 0, n, nv, e->og, nv, s))) return rc;
-    return launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
+    mark(e, "latent.gate");
+    rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
+    mark(e, "latent.out_gemm");
+    return rc;
 }
 
 int run_delta(wf_seq_engine* e, LayerState& L, const Batch& b) {
@@ -235,6 +255,7 @@ int run_delta(wf_seq_engine* e, LayerState& L, const Batch& b) {
     int rc;
     DeltaDims D{H, c.kv_heads, c.dim, c.vdim};
     if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q | k | v | g | b | a]
+    mark(e, "delta.proj_gemm");
     float* st_conv = e->state + L.st_conv;
     if ((rc = launch_causal_taps(e->dt, b, e->proj, L.np, L.conv_w, c.conv, C, st_conv, e->slot_stride, 0, 1, nullptr, 0, e->qkvc, C, s))) return rc;
     if ((rc = launch_taps_state(b, e->proj, L.np, c.conv, C, st_conv, e->slot_stride, s))) return rc;
@@ -242,9 +263,14 @@ int run_delta(wf_seq_engine* e, LayerState& L, const Batch& b) {
     const float* b_raw = g_raw + nv;
     const float* a_raw = b_raw + H;
     if ((rc = launch_delta_prep(e->dt, D, n, e->qkvc, C, a_raw, L.np, b_raw, L.np, L.A_log, L.dt_bias, e->beta, e->decay, s))) return rc;
+    mark(e, "delta.conv+prep");
     if ((rc = launch_delta_rule(b, D, e->qkvc, C, e->beta, e->decay, e->state + L.st_S, e->slot_stride, e->od, s))) return rc;
+    mark(e, "delta.rule");
     if ((rc = launch_delta_post(e->dt, D, n, e->od, L.onorm, e->cfg.eps, g_raw, L.np, e->og, s))) return rc;
-    return launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
+    mark(e, "delta.post");
+    rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
+    mark(e, "delta.out_gemm");
+    return rc;
 }
 
 int run_mixer(wf_seq_engine* e, LayerState& L, const Batch& b) {
@@ -258,20 +284,47 @@ int run_ff(wf_seq_engine* e, LayerState& L, const Batch& b) {
     int rc;
     RouterDims R{c.experts, c.identity, c.top, c.groups, c.keep};
     if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.router, W, e->z, 1, N, n, N, W), s))) return rc;
+    mark(e, "moe.router");
     if (c.experts > 0 && cuda_check(cudaMemsetAsync(e->counts, 0, (size_t)c.experts * 4, s), "counts")) return WF_ERR_CUDA;
     if ((rc = launch_moe_route(e->dt, R, n, e->z, N, L.correction, e->ids, e->wts, e->counts, s))) return rc;
+    mark(e, "moe.router");
+    const int pairs = n * c.top;
+    GemmArgs gp = lin(e->h_t, 0, W, L.wgu, W, e->gu, 1, 2 * c.ff, pairs, 2 * c.ff, W);
+    gp.group_stride = (long long)2 * c.ff * W;
+    GemmArgs gd = lin(e->hmid, 0, c.ff, L.wd, c.ff, e->yexp, 1, W, pairs, W, c.ff);
+    gd.group_stride = (long long)W * c.ff;
+    if (c.experts > 0 && pairs <= e->pair_path_max && gemv_pairs_usable(e->dt, gp) && gemv_pairs_usable(e->dt, gd)) {
+        // few tokens (decoding): one weight-streaming product per (token, expert) pair, no sorting
+        if ((rc = launch_gemv_pairs(e->dt, gp, e->ids, c.experts, pairs, c.top, s))) return rc;
+        mark(e, "moe.gate_up");
+        if ((rc = launch_silu_mul(e->dt, e->gu, pairs, c.ff, nullptr, e->hmid, s))) return rc;
+        mark(e, "moe.silu_mul");
+        if ((rc = launch_gemv_pairs(e->dt, gd, e->ids, c.experts, pairs, 1, s))) return rc;
+        mark(e, "moe.down");
+        rc = launch_moe_combine(e->dt, R, n, W, e->ids, e->wts, nullptr, e->yexp, e->h_t, e->y, s);
+        mark(e, "moe.combine");
+        return rc;
+    }
     if (c.experts > 0) {
         const int P = (n * c.top + GEMM_BM - 1) / GEMM_BM * GEMM_BM + c.experts * GEMM_BM;
         if ((rc = launch_moe_plan(R, n, e->ids, e->counts, e->plan_scratch, e->sorted_rows, e->pair_row, e->tile_group, P, s))) return rc;
-        GemmArgs g = lin(e->h_t, 0, W, L.wgu, W, e->gu, 1, 2 * c.ff, P, 2 * c.ff, W);
-        g.tile_group = e->tile_group; g.group_stride = (long long)2 * c.ff * W; g.a_rows = e->sorted_rows;
+        mark(e, "moe.plan");
+        // the experts' input rows, expert after expert (a dense operand for the tensor-core product)
+        if ((rc = launch_gather_rows(e->dt, e->h_t, W, e->sorted_rows, P, W, e->hperm, s))) return rc;
+        GemmArgs g = lin(e->hperm, 0, W, L.wgu, W, e->gu, 1, 2 * c.ff, P, 2 * c.ff, W);
+        g.tile_group = e->tile_group; g.group_stride = (long long)2 * c.ff * W; g.n_groups = c.experts;
         if ((rc = launch_gemm(e->dt, g, s))) return rc;
+        mark(e, "moe.gate_up");
         if ((rc = launch_silu_mul(e->dt, e->gu, P, c.ff, e->tile_group, e->hmid, s))) return rc;
+        mark(e, "moe.silu_mul");
         GemmArgs g2 = lin(e->hmid, 0, c.ff, L.wd, c.ff, e->yexp, 1, W, P, W, c.ff);
-        g2.tile_group = e->tile_group; g2.group_stride = (long long)W * c.ff;
+        g2.tile_group = e->tile_group; g2.group_stride = (long long)W * c.ff; g2.n_groups = c.experts;
         if ((rc = launch_gemm(e->dt, g2, s))) return rc;
+        mark(e, "moe.down");
     }
-    return launch_moe_combine(e->dt, R, n, W, e->ids, e->wts, e->pair_row, e->yexp, e->h_t, e->y, s);
+    rc = launch_moe_combine(e->dt, R, n, W, e->ids, e->wts, e->pair_row, e->yexp, e->h_t, e->y, s);
+    mark(e, "moe.combine");
+    return rc;
 }
 
 // norm -> input convolution (state rolled forward) -> e->h_t
@@ -281,7 +334,9 @@ int run_input(wf_seq_engine* e, const Batch& b, const void* norm_w, const void* 
     int rc;
     if ((rc = launch_group_rmsnorm(e->dt, e->x, W, norm_w, e->cfg.norm_groups, e->cfg.eps, b.n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s))) return rc;
     if ((rc = launch_causal_taps(e->dt, b, e->hn, W, canon_w, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, 1, 0, e->h_t, W, nullptr, 0, s))) return rc;
-    return launch_taps_state(b, e->hn, W, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, s);
+    rc = launch_taps_state(b, e->hn, W, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, s);
+    mark(e, "norm+input_conv");
+    return rc;
 }
 
 int run_layers(wf_seq_engine* e, const StepView& v) {
@@ -289,15 +344,18 @@ int run_layers(wf_seq_engine* e, const StepView& v) {
     cudaStream_t s = e->stream;
     int rc;
     if ((rc = launch_embed_f32(e->dt, e->embed, v.tokens, n, W, e->x, s))) return rc;
+    mark(e, "embed");
     for (int li = 0; li < e->cfg.n_layers; ++li) {
         LayerState& L = e->layers[li];
         if ((rc = run_input(e, v.b, L.norm1, L.canon1, L.st_canon1))) return rc;
         if ((rc = run_mixer(e, L, v.b))) return rc;
         if ((rc = launch_group_rmsnorm(e->dt, e->y, W, L.norm1b, e->cfg.norm_groups, e->cfg.eps, n, W, e->x, e->x, W, nullptr, 0, nullptr, s))) return rc;
+        mark(e, "norm+residual");
         if (L.c.has_ff) {
             if ((rc = run_input(e, v.b, L.norm2, L.canon2, L.st_canon2))) return rc;
             if ((rc = run_ff(e, L, v.b))) return rc;
             if ((rc = launch_group_rmsnorm(e->dt, e->y, W, L.norm2b, e->cfg.norm_groups, e->cfg.eps, n, W, e->x, e->x, W, nullptr, 0, nullptr, s))) return rc;
+            mark(e, "norm+residual");
         }
         if (e->layer_tap) {
             if (cuda_check(cudaMemcpyAsync(e->layer_tap + (size_t)li * n * W, e->x, (size_t)n * W * 4, cudaMemcpyDeviceToHost, s), "layer tap")) return WF_ERR_CUDA;
@@ -322,7 +380,9 @@ int run_head(wf_seq_engine* e, const StepView& v, int nwant) {
     int rc;
     if ((rc = ensure_logits(e, nwant))) return rc;
     if ((rc = launch_group_rmsnorm(e->dt, e->x, W, e->final_norm, e->cfg.norm_groups, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream))) return rc;
-    return launch_gemm(e->dt, lin(e->xn, 0, W, e->head, W, e->logits, 1, e->cfg.vocab, nwant, e->cfg.vocab, W), e->stream);
+    rc = launch_gemm(e->dt, lin(e->xn, 0, W, e->head, W, e->logits, 1, e->cfg.vocab, nwant, e->cfg.vocab, W), e->stream);
+    mark(e, "final_norm+head_gemm");
+    return rc;
 }
 
 }  // namespace
@@ -344,6 +404,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     e->cfg = *cfg;
     e->dt = cfg->dtype == WF_SEQ_F32 ? WF_F32 : WF_BF16;
     e->esz = e->dt == WF_F32 ? 4 : 2;
+    if (const char* pm = getenv("WF_SEQ_PAIR_MAX")) e->pair_path_max = atoi(pm);
     const wf_seq_config& c = e->cfg;
     const int W = c.width, T = c.max_step_tokens, taps = c.canon_taps;
     int rc = WF_OK;
@@ -458,9 +519,11 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     TRY(dalloc_n(e, &e->pair_row, (size_t)T * max_top)); TRY(dalloc_n(e, &e->counts, max_E)); TRY(dalloc_n(e, &e->plan_scratch, 2 * max_E + 1));
     const size_t P = e->P ? e->P : GEMM_BM;
     TRY(dalloc_n(e, &e->sorted_rows, P)); TRY(dalloc_n(e, &e->tile_group, P / GEMM_BM));
+    TRY(dalloc_t(e, &e->hperm, P * W));
     TRY(dalloc_n(e, &e->gu, P * 2 * max_ff)); TRY(dalloc_t(e, &e->hmid, P * max_ff)); TRY(dalloc_n(e, &e->yexp, P * W));
 #undef TRY
     if (cuda_check(cudaMemsetAsync(e->state, 0, e->slot_stride * c.slots * 4, e->stream), "state")) { wf_seq_destroy(e); return WF_ERR_CUDA; }
+    if (cuda_check(cudaMemsetAsync(e->pool, 0, (size_t)std::max<long long>(cache_elems, 1) * c.max_pages * e->esz, e->stream), "pool")) { wf_seq_destroy(e); return WF_ERR_CUDA; }
     if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) { wf_seq_destroy(e); return WF_ERR_CUDA; }
     *out = e;
     return WF_OK;
@@ -550,6 +613,7 @@ extern "C" int wf_seq_step(wf_seq_engine* e, int nseq, const int32_t* slots, con
     if (logits_host && nwant > 0)
         if (cuda_check(cudaMemcpyAsync(logits_host, e->logits, (size_t)nwant * e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream), "logits D2H")) return WF_ERR_CUDA;
     if (cuda_check(cudaStreamSynchronize(e->stream), "wf_seq_step")) return WF_ERR_CUDA;
+    if (e->dt == WF_BF16 && gemm_tc_error(e->stream)) { set_error("wf_seq_step: a bounded wait of the tensor-core matrix product ran out"); return WF_ERR_CUDA; }
     commit_lengths(e, nseq, slots, counts);
     return WF_OK;
 }
@@ -605,6 +669,49 @@ extern "C" int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, 
     if (cuda_check(cudaMemcpyAsync(out_host, result, bytes, cudaMemcpyDeviceToHost, s), "out")) return WF_ERR_CUDA;
     if (cuda_check(cudaStreamSynchronize(s), "wf_seq_run_part")) return WF_ERR_CUDA;
     commit_lengths(e, nseq, slots, counts);
+    return WF_OK;
+}
+
+extern "C" int wf_seq_time_step(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t* counts, int iters, float* ms_out);
+
+extern "C" int wf_seq_set_length(wf_seq_engine* e, int slot, int len) {
+    if (!e || slot < 0 || slot >= e->cfg.slots || !e->pt.live[slot] || len < 0) { set_error("wf_seq_set_length: bad slot / length"); return WF_ERR_INVALID; }
+    e->pt.truncate(slot, len);
+    if (!e->pt.ensure(slot, len)) { set_error("wf_seq_set_length: cache pool exhausted"); return WF_ERR_INVALID; }
+    e->h_len[slot] = len;
+    return WF_OK;
+}
+
+extern "C" int wf_seq_profile_step(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t* counts, int iters, char* out, size_t cap) {
+    if (!e || !out || cap < 64) { set_error("wf_seq_profile_step: bad argument"); return WF_ERR_INVALID; }
+    e->prof = true;
+    e->marks.clear();
+    float ms = 0.f;
+    mark(e, "start");
+    const int rc = wf_seq_time_step(e, nseq, slots, counts, iters, &ms);
+    e->prof = false;
+    std::map<std::string, std::pair<double, int>> acc;
+    if (!rc) {
+        // the first (untimed) pass of wf_seq_time_step is included: iters + 1 passes
+        for (size_t i = 1; i < e->marks.size(); ++i) {
+            float t = 0.f;
+            cudaEventElapsedTime(&t, e->marks[i - 1].second, e->marks[i].second);
+            auto& a = acc[e->marks[i].first];
+            a.first += t; a.second += 1;
+        }
+    }
+    for (auto& m : e->marks) cudaEventDestroy(m.second);
+    e->marks.clear();
+    if (rc) return rc;
+    std::string js = "{";
+    char buf[160];
+    for (auto& kv : acc) {
+        snprintf(buf, sizeof buf, "%s\"%s\": [%.6f, %d]", js.size() > 1 ? ", " : "", kv.first.c_str(), kv.second.first / (iters + 1), kv.second.second / (iters + 1));
+        js += buf;
+    }
+    js += "}";
+    if (js.size() + 1 > cap) { set_error("wf_seq_profile_step: output buffer too small"); return WF_ERR_INVALID; }
+    memcpy(out, js.c_str(), js.size() + 1);
     return WF_OK;
 }
 

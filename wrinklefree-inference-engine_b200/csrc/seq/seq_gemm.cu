@@ -11,7 +11,7 @@ namespace seq {
 
 namespace {
 
-constexpr int BM = GEMM_BM, BN = 64, BK = 16;
+constexpr int BM = 64, BN = 64, BK = 16;       // kernel tile; GEMM_BM (the grouped form's row granule) is a multiple of BM
 
 template <typename T, bool AF32, bool CF32>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmArgs g) {
@@ -20,7 +20,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmArgs g) {
     const int tile_m = blockIdx.y, tile_n = blockIdx.x, z = blockIdx.z;
     long long grp = 0;
     if (g.tile_group) {
-        const int e = g.tile_group[tile_m];
+        const int e = g.tile_group[tile_m * BM / GEMM_BM];
         if (e < 0) return;
         grp = (long long)e * g.group_stride;
     }
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(128) gemm_mma_kernel(GemmArgs g) {
     const int tile_m = blockIdx.y, tile_n = blockIdx.x, z = blockIdx.z;
     long long grp = 0;
     if (g.tile_group) {
-        const int e = g.tile_group[tile_m];
+        const int e = g.tile_group[tile_m * BM / GEMM_BM];
         if (e < 0) return;
         grp = (long long)e * g.group_stride;
     }
@@ -212,29 +212,157 @@ __global__ void __launch_bounds__(128) gemm_mma_kernel(GemmArgs g) {
             }
 }
 
+// ---- few-row form (decoding): the weight matrix is streamed once, 16 bytes per lane per load; a warp owns GV_RPW output columns and
+// all MR <= 8 activation rows, which every warp re-reads through L1.  With `pair_expert` set, grid.y walks (token, expert) pairs instead:
+// pair p multiplies ONE activation row (p / pair_div) with the weight matrix of expert pair_expert[p] (routed experts while decoding).
+constexpr int GV_WARPS = 8, GV_RPW = 2;
+
+template <typename T> struct Vec16;
+template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
+template <> struct Vec16<float> { static constexpr int N = 4; };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float (&out)[Vec16<T>::N]);
+template <>
+__device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_bfloat16* p, float (&out)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { out[2 * i] = __uint_as_float(w[i] << 16); out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+template <>
+__device__ __forceinline__ void load_vec<float>(const float* p, float (&out)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+
+struct PairArgs { const int32_t* pair_expert; int n_experts; int pair_div; };
+
+template <typename T, int MR, bool AF32, bool CF32>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_rows_kernel(GemmArgs g, PairArgs pa) {
+    constexpr int VN = Vec16<T>::N;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const T* B = (const T*)g.B;
+    int a_row0 = 0, c_row0 = 0, rows = g.M;
+    if (pa.pair_expert) {
+        const int pr = blockIdx.y;
+        const int e = pa.pair_expert[pr];
+        if (e < 0 || e >= pa.n_experts) return;
+        B += (long long)e * g.group_stride;
+        a_row0 = pr / pa.pair_div; c_row0 = pr; rows = 1;
+    }
+    const int n0 = (blockIdx.x * GV_WARPS + warp) * GV_RPW;
+    if (n0 >= g.N) return;
+    float acc[GV_RPW][MR];
+#pragma unroll
+    for (int r = 0; r < GV_RPW; ++r)
+#pragma unroll
+        for (int m = 0; m < MR; ++m) acc[r][m] = 0.f;
+    const int kvec = g.K / VN;                       // the launcher guarantees K % VN == 0 and 16-byte aligned rows
+    for (int kv = lane; kv < kvec; kv += 32) {
+        const int k = kv * VN;
+        float b[GV_RPW][VN];
+#pragma unroll
+        for (int r = 0; r < GV_RPW; ++r) {
+            const int n = n0 + r < g.N ? n0 + r : g.N - 1;
+            load_vec<T>(B + (size_t)n * g.ldb + k, b[r]);
+        }
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+            if (m < rows) {
+                float a[VN];
+                if (AF32) {
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) a[i] = ((const float*)g.A)[(size_t)(a_row0 + m) * g.lda + k + i];
+                } else {
+                    load_vec<T>((const T*)g.A + (size_t)(a_row0 + m) * g.lda + k, a);
+                }
+#pragma unroll
+                for (int r = 0; r < GV_RPW; ++r)
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) acc[r][m] = fmaf(a[i], b[r][i], acc[r][m]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < GV_RPW; ++r)
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+            float v = acc[r][m];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && m < rows && n0 + r < g.N) {
+                const size_t off = (size_t)(c_row0 + m) * g.ldc + n0 + r;
+                if (CF32) ((float*)g.C)[off] = v; else ((T*)g.C)[off] = from_f<T>(v);
+            }
+        }
+}
+
+template <typename T, int MR>
+void gemv_dispatch(const GemmArgs& g, const PairArgs& pa, dim3 grid, cudaStream_t s) {
+    if (g.a_f32) { if (g.c_f32) gemv_rows_kernel<T, MR, true, true><<<grid, GV_WARPS * 32, 0, s>>>(g, pa); else gemv_rows_kernel<T, MR, true, false><<<grid, GV_WARPS * 32, 0, s>>>(g, pa); }
+    else { if (g.c_f32) gemv_rows_kernel<T, MR, false, true><<<grid, GV_WARPS * 32, 0, s>>>(g, pa); else gemv_rows_kernel<T, MR, false, false><<<grid, GV_WARPS * 32, 0, s>>>(g, pa); }
+}
+
+template <typename T>
+bool gemv_ok(const GemmArgs& g) {
+    constexpr int VN = Vec16<T>::N;
+    const size_t ea = g.a_f32 ? 4 : sizeof(T);
+    return g.K % VN == 0 && g.ldb % VN == 0 && (((uintptr_t)g.B) & 15) == 0 && (g.lda * ea) % 16 == 0 && (((uintptr_t)g.A) & 15) == 0 &&
+           (g.group_stride * (long long)sizeof(T)) % 16 == 0;
+}
+
+template <typename T>
+void gemv_launch(const GemmArgs& g, const PairArgs& pa, int rows, int ny, cudaStream_t s) {
+    dim3 grid((g.N + GV_WARPS * GV_RPW - 1) / (GV_WARPS * GV_RPW), ny);
+    if (rows <= 1) gemv_dispatch<T, 1>(g, pa, grid, s);
+    else if (rows <= 2) gemv_dispatch<T, 2>(g, pa, grid, s);
+    else if (rows <= 4) gemv_dispatch<T, 4>(g, pa, grid, s);
+    else gemv_dispatch<T, 8>(g, pa, grid, s);
+}
+
 template <typename T>
 void simt_dispatch(const GemmArgs& g, dim3 grid, cudaStream_t s) {
     if (g.a_f32) { if (g.c_f32) gemm_simt_kernel<T, true, true><<<grid, 256, 0, s>>>(g); else gemm_simt_kernel<T, true, false><<<grid, 256, 0, s>>>(g); }
     else { if (g.c_f32) gemm_simt_kernel<T, false, true><<<grid, 256, 0, s>>>(g); else gemm_simt_kernel<T, false, false><<<grid, 256, 0, s>>>(g); }
 }
 
-int g_force_simt = -1;
+int g_force_simt = -1, g_tc_min = -1;
 
 }  // namespace
 
 int launch_gemm(int dt, const GemmArgs& g, cudaStream_t s) {
     if (g.M <= 0 || g.N <= 0 || g.batch <= 0) return WF_OK;
     if (g.K <= 0 || !g.A || !g.B || !g.C) { set_error("gemm: bad arguments (M %d N %d K %d)", g.M, g.N, g.K); return WF_ERR_INVALID; }
+    if (g_tc_min < 0) { const char* e = getenv("WF_SEQ_TC_MIN"); g_tc_min = e ? atoi(e) : 17; }
     if (g_force_simt < 0) { const char* e = getenv("WF_SEQ_GEMM_SIMT"); g_force_simt = (e && atoi(e)) ? 1 : 0; }
+    if (g.M <= 8 && g.batch == 1 && !g.tile_group && !g.a_rows) {      // decoding: stream the weights once
+        const PairArgs none{nullptr, 0, 1};
+        if (dt == WF_F32 && gemv_ok<float>(g)) { gemv_launch<float>(g, none, g.M, 1, s); return launch_check(cudaGetLastError(), "gemv_rows"); }
+        if (dt == WF_BF16 && gemv_ok<__nv_bfloat16>(g)) { gemv_launch<__nv_bfloat16>(g, none, g.M, 1, s); return launch_check(cudaGetLastError(), "gemv_rows"); }
+    }
     dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, g.batch);
     if (grid.y > 65535u || grid.z > 65535u) { set_error("gemm: grid too large"); return WF_ERR_UNSUPPORTED; }
     if (dt == WF_F32) simt_dispatch<float>(g, grid, s);
     else if (g_force_simt) simt_dispatch<__nv_bfloat16>(g, grid, s);
+    else if (g.M >= g_tc_min && gemm_tc_usable(g)) return launch_gemm_tc(g, g.n_groups, s);
     else {
         if (g.a_f32) { if (g.c_f32) gemm_mma_kernel<true, true><<<grid, 128, 0, s>>>(g); else gemm_mma_kernel<true, false><<<grid, 128, 0, s>>>(g); }
         else { if (g.c_f32) gemm_mma_kernel<false, true><<<grid, 128, 0, s>>>(g); else gemm_mma_kernel<false, false><<<grid, 128, 0, s>>>(g); }
     }
     return launch_check(cudaGetLastError(), "gemm");
+}
+
+bool gemv_pairs_usable(int dt, const GemmArgs& g) {
+    return dt == WF_F32 ? gemv_ok<float>(g) : gemv_ok<__nv_bfloat16>(g);
+}
+
+int launch_gemv_pairs(int dt, const GemmArgs& g, const int32_t* pair_expert, int n_experts, int pairs, int pair_div, cudaStream_t s) {
+    if (pairs <= 0 || g.N <= 0) return WF_OK;
+    if (pairs > 65535 || !gemv_pairs_usable(dt, g)) { set_error("gemv_pairs: unsupported shape"); return WF_ERR_UNSUPPORTED; }
+    const PairArgs pa{pair_expert, n_experts, pair_div};
+    if (dt == WF_F32) gemv_launch<float>(g, pa, 1, pairs, s); else gemv_launch<__nv_bfloat16>(g, pa, 1, pairs, s);
+    return launch_check(cudaGetLastError(), "gemv_pairs");
 }
 
 }  // namespace seq

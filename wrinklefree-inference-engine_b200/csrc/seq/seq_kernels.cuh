@@ -32,14 +32,25 @@ struct GemmArgs {
     int M = 0, N = 0, K = 0;
     int batch = 1;                           // grid.z problems with element strides sA, sB, sC
     long long sA = 0, sB = 0, sC = 0;
-    // grouped form (routed experts): row tile t (GEMM_BM rows) uses weight tile_group[t] (B + group * group_stride), or is skipped when < 0;
+    // grouped form (routed experts): rows [t * GEMM_BM, (t + 1) * GEMM_BM) use weight tile_group[t] (B + group * group_stride), or are skipped when < 0;
     // a_rows (optional) gathers A rows (-1 = a zero row).  M is then the padded row count bound; m_dev (optional) the real one on the device.
     const int32_t* tile_group = nullptr;
     long long group_stride = 0;
     const int32_t* a_rows = nullptr;
+    int n_groups = 1;                        // weight matrices stacked behind B (grouped form)
 };
-constexpr int GEMM_BM = 64;
+constexpr int GEMM_BM = 128;                 // row granule of the grouped form (the token tile of the tcgen05 kernel)
 int launch_gemm(int dt, const GemmArgs& g, cudaStream_t s);
+// tcgen05 form (seq_gemm_tc.cu): bf16 operands, dense A rows; launch_gemm picks it from WF_SEQ_TC_MIN (17) rows up
+bool gemm_tc_usable(const GemmArgs& g);
+int launch_gemm_tc(const GemmArgs& g, int n_groups, cudaStream_t s);
+int gemm_tc_error(cudaStream_t s);           // 0 = no bounded wait of the tcgen05 kernel ever ran out on this device
+// dst T [P, W] = src T [rows[i], :] (zero rows where rows[i] < 0)
+int launch_gather_rows(int dt, const void* src, int ld, const int32_t* rows, int P, int W, void* dst, cudaStream_t s);
+// routed experts while decoding: pair p (p < pairs) computes C[p, :] = B[pair_expert[p]] . A[p / pair_div, :]  (skipped when pair_expert[p]
+// is not in [0, n_experts)); B + expert * g.group_stride is that expert's [N, K] matrix.  Needs 16-byte aligned rows (gemv_pairs_usable).
+bool gemv_pairs_usable(int dt, const GemmArgs& g);
+int launch_gemv_pairs(int dt, const GemmArgs& g, const int32_t* pair_expert, int n_experts, int pairs, int pair_div, cudaStream_t s);
 
 // ---- latent attention ---------------------------------------------------------------------------------------------------
 struct LatentDims { int H, d, r, dv, R; float scale, rope_base; int rope_dims, window; };
@@ -81,8 +92,8 @@ int launch_moe_route(int dt, const RouterDims& R, int n, const float* z, int ldz
 int launch_moe_plan(const RouterDims& R, int n, const int32_t* ids, const int32_t* counts, int32_t* scratch, int32_t* sorted_rows,
                     int32_t* pair_row, int32_t* tile_group, int P, cudaStream_t s);
 // hmid T [P, ff] = silu(gu[:, :ff]) * gu[:, ff:]   (gu float [P, 2 ff]); rows of skipped tiles are left alone
-int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s);
-// out float [n, W] = sum_k wts[t, k] * (ids[t, k] < E ? y[pair_row[t, k], :] : h[t, :])     (h T [n, W])
+int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s);   // tile_group null: every row
+// out float [n, W] = sum_k wts[t, k] * (ids[t, k] < E ? y[pair_row[t, k], :] : h[t, :])     (h T [n, W]; pair_row null: row t * top + k)
 int launch_moe_combine(int dt, const RouterDims& R, int n, int W, const int32_t* ids, const float* wts, const int32_t* pair_row, const float* y,
                        const void* h, float* out, cudaStream_t s);
 

@@ -112,7 +112,8 @@ __global__ void moe_combine_kernel(RouterDims R, int W, const int32_t* __restric
         for (int k = 0; k < R.top; ++k) {
             const int e = ids[(size_t)i * R.top + k];
             const float w = wts[(size_t)i * R.top + k];
-            const float v = e < R.E ? y[(size_t)pair_row[(size_t)i * R.top + k] * W + c] : to_f(h[(size_t)i * W + c]);
+            const size_t pi = (size_t)i * R.top + k;
+            const float v = e < R.E ? y[(size_t)(pair_row ? pair_row[pi] : (int)pi) * W + c] : to_f(h[(size_t)i * W + c]);
             acc = fmaf(w, v, acc);
         }
         out[(size_t)i * W + c] = acc;
@@ -194,23 +195,32 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
     float z = 0.f;
     for (int c = tid; c < V; c += SM_THREADS) z += expf((row[c] - bv) * it);
     z = block_reduce_sum(z, scratch);
-    // bisection on tau in (0, 1]: unnormalised weight w_c = exp((x_c - max) / T) in (0, 1]
-    float lo = 0.f, hi = 1.f;                        // keep {w >= tau}; tau = lo keeps everything
-    const bool limit = (top_k > 0 && top_k < V) || (top_p > 0.f && top_p < 1.f);
-    if (limit) {
-        for (int it_ = 0; it_ < 30; ++it_) {
-            const float tau = 0.5f * (lo + hi);
-            float cnt = 0.f, mass = 0.f;
-            for (int c = tid; c < V; c += SM_THREADS) { const float w = expf((row[c] - bv) * it); if (w >= tau) { cnt += 1.f; mass += w; } }
+    // thresholds on the unnormalised weight w_c = exp((x_c - max) / T) in (0, 1], each found by bisection:
+    // tau_k = the smallest threshold that keeps at most top_k entries, tau_p = the largest one whose kept mass still reaches top_p
+    const bool k_active = top_k > 0 && top_k < V, p_active = top_p > 0.f && top_p < 1.f;
+    float tau = 0.f;
+    if (k_active) {
+        float lo = 0.f, hi = 1.f;                    // {w >= hi} always fits (the maximum alone, w = 1)
+        for (int r = 0; r < 30; ++r) {
+            const float mid = 0.5f * (lo + hi);
+            float cnt = 0.f;
+            for (int c = tid; c < V; c += SM_THREADS) cnt += expf((row[c] - bv) * it) >= mid ? 1.f : 0.f;
             cnt = block_reduce_sum(cnt, scratch);
-            mass = block_reduce_sum(mass, scratch);
-            const bool k_ok = !(top_k > 0 && top_k < V) || cnt <= (float)top_k;
-            const bool p_reached = !(top_p > 0.f && top_p < 1.f) || mass >= top_p * z;
-            // raise tau while the set is still too large for top_k, or still reaches top_p (a smaller set may do)
-            if (!k_ok || (p_reached && cnt > 1.f)) lo = tau; else hi = tau;
+            if (cnt <= (float)top_k) hi = mid; else lo = mid;
         }
+        tau = hi;
     }
-    const float tau = limit ? lo : 0.f;
+    if (p_active) {
+        float lo = 0.f, hi = 1.f;                    // {w >= lo} always reaches the mass (everything)
+        for (int r = 0; r < 30; ++r) {
+            const float mid = 0.5f * (lo + hi);
+            float mass = 0.f;
+            for (int c = tid; c < V; c += SM_THREADS) { const float w = expf((row[c] - bv) * it); if (w >= mid) mass += w; }
+            mass = block_reduce_sum(mass, scratch);
+            if (mass >= top_p * z) lo = mid; else hi = mid;
+        }
+        tau = fmaxf(tau, lo);
+    }
     // kept mass per thread over a contiguous chunk, then the draw
     const int chunk = (V + SM_THREADS - 1) / SM_THREADS;
     const int c0 = tid * chunk, c1 = c0 + chunk < V ? c0 + chunk : V;

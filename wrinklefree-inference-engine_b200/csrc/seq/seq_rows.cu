@@ -121,6 +121,19 @@ int launch_gate_mul(int dt, const float* x, int ldx, const float* g, int ldg, in
 }
 
 template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, int ld, const int32_t* __restrict__ rows, int W, T* __restrict__ dst) {
+    const int i = blockIdx.x, r = rows[i];
+    for (int c = threadIdx.x; c < W; c += blockDim.x) dst[(size_t)i * W + c] = r >= 0 ? src[(size_t)r * ld + c] : from_f<T>(0.f);
+}
+
+int launch_gather_rows(int dt, const void* src, int ld, const int32_t* rows, int P, int W, void* dst, cudaStream_t s) {
+    if (P <= 0) return WF_OK;
+    if (dt == WF_BF16) gather_rows_kernel<<<P, 256, 0, s>>>((const __nv_bfloat16*)src, ld, rows, W, (__nv_bfloat16*)dst);
+    else gather_rows_kernel<<<P, 256, 0, s>>>((const float*)src, ld, rows, W, (float*)dst);
+    return launch_check(cudaGetLastError(), "gather_rows");
+}
+
+template <typename T>
 __global__ void transpose_heads_kernel(const T* __restrict__ in, int R, int C, T* __restrict__ out) {
     const size_t h = blockIdx.y;
     for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < R * C; idx += gridDim.x * blockDim.x) {

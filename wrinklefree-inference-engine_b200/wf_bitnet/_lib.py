@@ -157,6 +157,8 @@ SEQ_SYMBOLS = {
     "wf_seq_set_layer_tap": (_i, [_vp, _vp]),
     "wf_seq_run_part": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "wf_seq_time_step": (_i, [_vp, _i, _vp, _vp, _i, _fp]),
+    "wf_seq_profile_step": (_i, [_vp, _i, _vp, _vp, _i, C.c_char_p, _sz]),
+    "wf_seq_set_length": (_i, [_vp, _i, _i]),
 }
 _seq_lib = None
 

@@ -127,3 +127,14 @@ class SeqEngine:
         ms = C.c_float()
         seq_check(seq_lib().wf_seq_time_step(self._h, s.size, s.ctypes.data, c.ctypes.data, iters, C.byref(ms)))
         return float(ms.value)
+
+    def profile_step(self, slots, counts, iters: int = 5) -> dict:
+        """{launch group: (ms per step, launch groups per step)} with an event after every launch group (slower than time_step)."""
+        import json
+        s, c = _i32(slots), _i32(counts)
+        buf = C.create_string_buffer(1 << 16)
+        seq_check(seq_lib().wf_seq_profile_step(self._h, s.size, s.ctypes.data, c.ctypes.data, iters, buf, len(buf)))
+        return {k: tuple(v) for k, v in json.loads(buf.value.decode()).items()}
+
+    def set_length(self, slot: int, length: int) -> None:
+        seq_check(seq_lib().wf_seq_set_length(self._h, slot, length))
