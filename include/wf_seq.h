@@ -87,6 +87,12 @@ int wf_seq_profile_step(wf_seq_engine* e, int nseq, const int32_t* slots, const 
 /* measurement: declare that a live slot holds `len` tokens (pages are allocated, their contents are whatever the pool holds) */
 int wf_seq_set_length(wf_seq_engine* e, int slot, int len);
 
+/* The engine's matrix product on its own: C[m, n] = sum_k A[m, k] * B[n, k] (device pointers; A is dtype or float, C float or dtype).
+ * tile_group (optional): expert of every 128-row tile of A / C (< 0: skipped), experts' [N, K] matrices group_stride elements apart.
+ * algo: 0 as the engine chooses, 1 plain FMA, 2 mma.sync, 3 tcgen05, 4 few-row streaming. */
+int wf_seq_op_gemm(int dtype, const void* A, int a_f32, int lda, const void* B, int ldb, void* C, int c_f32, int ldc, int M, int N, int K,
+                   const int32_t* tile_group, long long group_stride, int n_groups, int algo, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

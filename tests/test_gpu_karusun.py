@@ -427,3 +427,50 @@ def test_registry_and_config_reader():
     assert registry.resolve({"architectures": ["BitNetForCausalLM"]}).__name__ == "BitNetForCausalLM"
     with pytest.raises(KeyError):
         registry.resolve({"architecture": "Nope"})
+
+
+# ---------------------------------------------------------------------------------------------------------------- matrix products
+def _gemm(dtype, A, B, M, N, K, algo, tile_group=None, group_stride=0, n_groups=1, c_f32=True):
+    from wf_bitnet._lib import seq_check, seq_lib
+    C_ = torch.full((M, N), float("nan"), dtype=torch.float32 if c_f32 else A.dtype, device="cuda")
+    tg = tile_group.data_ptr() if tile_group is not None else None
+    seq_check(seq_lib().wf_seq_op_gemm(1 if dtype == torch.bfloat16 else 0, A.data_ptr(), 1 if (A.dtype == torch.float32 and dtype == torch.bfloat16) else 0,
+                                       A.stride(0), B.data_ptr(), B.stride(-2), C_.data_ptr(), 1 if c_f32 else 0, N, M, N, K, tg, group_stride, n_groups, algo,
+                                       torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    return C_
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (5, 300, 200), (8, 1000, 2560), (17, 72, 48), (130, 257, 96), (300, 1000, 2560), (1100, 640, 520)])
+def test_matrix_product_forms_agree(M, N, K):
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
+    A = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    B = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    want = A.double() @ B.double().T
+    for algo in (1, 2, 3) + ((4,) if M <= 8 else ()):
+        got = _gemm(torch.bfloat16, A, B, M, N, K, algo)
+        assert torch.isfinite(got).all(), algo
+        assert (got.double() - want).abs().max() < 2e-3 * (1 + want.abs().max()), (algo, M, N, K)
+    Af, Bf = A.float(), B.float()
+    for algo in (1,) + ((4,) if M <= 8 else ()):
+        got = _gemm(torch.float32, Af, Bf, M, N, K, algo)
+        assert (got.double() - want).abs().max() < 1e-4 * (1 + want.abs().max()), (algo, M, N, K)
+    out16 = _gemm(torch.bfloat16, A, B, M, N, K, 3, c_f32=False)
+    assert (out16.double() - want).abs().max() < 2e-2 * (1 + want.abs().max())
+
+
+def test_grouped_matrix_product_on_the_tensor_cores():
+    E, N, K, tiles = 5, 200, 192, 9
+    g = torch.Generator(device="cuda").manual_seed(3)
+    A = torch.randn(tiles * 128, K, device="cuda", generator=g).to(torch.bfloat16)
+    B = (torch.randn(E, N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    tg = torch.tensor([0, 0, 3, -1, 4, 1, -1, 2, 2], dtype=torch.int32, device="cuda")
+    for algo in (1, 2, 3):
+        got = _gemm(torch.bfloat16, A, B, tiles * 128, N, K, algo, tile_group=tg, group_stride=N * K, n_groups=E)
+        for t, e in enumerate(tg.tolist()):
+            rows = slice(t * 128, (t + 1) * 128)
+            if e < 0:
+                assert torch.isnan(got[rows]).all()          # skipped tiles are not touched
+            else:
+                want = A[rows].double() @ B[e].double().T
+                assert (got[rows].double() - want).abs().max() < 2e-3 * (1 + want.abs().max()), (algo, t)

@@ -72,6 +72,9 @@ struct wf_seq_engine {
     void *hperm = nullptr, *h_t = nullptr, *qn = nullptr, *olat = nullptr, *og = nullptr, *hmid = nullptr, *xn = nullptr;
     int32_t *ids = nullptr, *counts = nullptr, *plan_scratch = nullptr, *sorted_rows = nullptr, *pair_row = nullptr, *tile_group = nullptr;
     int P = 0;                        // padded expert-row bound
+    int attn_mma = 1;                 // latent attention on tensor cores where the sizes allow it (WF_SEQ_ATTN_MMA=0: the plain kernel)
+    float* attn_ws = nullptr;         // partial results of key-split attention
+    int attn_ws_rows = 0;             // token-splits it holds
     int pair_path_max = 64;           // up to this many (token, expert) pairs the experts run as per-pair weight streams (WF_SEQ_PAIR_MAX)
     float* logits = nullptr;
     size_t logits_rows = 0;
@@ -233,7 +236,19 @@ int run_latent(wf_seq_engine* e, LayerState& L, const Batch& b) {
         if ((rc = launch_gemm(e->dt, g, s))) return rc;
         mark(e, "latent.absorb_gemm");
     }
-    if ((rc = launch_latent_attn(e->dt, b, D, e->qa, e->qr, pc, e->olat, s))) return rc;
+    if (e->dt == WF_BF16 && e->attn_mma && latent_attn_mma_usable(D) && L.cache_off % 8 == 0 && e->page_stride % 8 == 0) {
+        // few query tokens and a long window: split the keys so that the machine is busy
+        int splits = 1;
+        const int span = c.window < e->cfg.max_pages * e->cfg.page_size ? c.window : e->cfg.max_pages * e->cfg.page_size;
+        if (n < 2 * sm_count()) {
+            splits = (2 * sm_count() + n - 1) / n;
+            if (splits > span / 128) splits = span / 128;
+            if (splits > e->attn_ws_rows / n) splits = e->attn_ws_rows / n;
+            if (splits > 16) splits = 16;
+            if (splits < 1) splits = 1;
+        }
+        if ((rc = launch_latent_attn_mma(b, D, e->qa, e->qr, pc, e->olat, e->attn_ws, splits, s))) return rc;
+    } else if ((rc = launch_latent_attn(e->dt, b, D, e->qa, e->qr, pc, e->olat, s))) return rc;
     mark(e, "latent.attention");
     {   // ov[i, h, :] = W_uv[h] olat[i, h, :]
         GemmArgs g = lin(e->olat, 0, H * c.kv_rank, L.uv, c.kv_rank, e->ov, 1, nv, n, c.vdim, c.kv_rank);
@@ -405,6 +420,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     e->dt = cfg->dtype == WF_SEQ_F32 ? WF_F32 : WF_BF16;
     e->esz = e->dt == WF_F32 ? 4 : 2;
     if (const char* pm = getenv("WF_SEQ_PAIR_MAX")) e->pair_path_max = atoi(pm);
+    if (const char* am = getenv("WF_SEQ_ATTN_MMA")) e->attn_mma = atoi(am);
     const wf_seq_config& c = e->cfg;
     const int W = c.width, T = c.max_step_tokens, taps = c.canon_taps;
     int rc = WF_OK;
@@ -513,6 +529,8 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     TRY(dalloc_n(e, &e->proj, (size_t)T * max_np));
     TRY(dalloc_t(e, &e->qn, (size_t)T * max_hd)); TRY(dalloc_n(e, &e->qr, (size_t)T * max_hrot)); TRY(dalloc_n(e, &e->qa, (size_t)T * max_hr));
     TRY(dalloc_t(e, &e->olat, (size_t)T * max_hr)); TRY(dalloc_n(e, &e->ov, (size_t)T * max_hv)); TRY(dalloc_t(e, &e->og, (size_t)T * max_hv));
+    e->attn_ws_rows = 4 * 148;
+    if (e->dt == WF_BF16 && max_hr > 1) TRY(dalloc_bytes(e, (void**)&e->attn_ws, (size_t)e->attn_ws_rows * (max_hr + 2 * max_H) * sizeof(float)));
     TRY(dalloc_n(e, &e->qkvc, (size_t)T * max_C)); TRY(dalloc_n(e, &e->beta, (size_t)T * max_H)); TRY(dalloc_n(e, &e->decay, (size_t)T * max_H));
     TRY(dalloc_n(e, &e->od, (size_t)T * max_hv));
     TRY(dalloc_n(e, &e->z, (size_t)T * max_N)); TRY(dalloc_n(e, &e->ids, (size_t)T * max_top)); TRY(dalloc_n(e, &e->wts, (size_t)T * max_top));

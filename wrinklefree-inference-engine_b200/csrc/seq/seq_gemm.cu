@@ -336,16 +336,19 @@ int launch_gemm(int dt, const GemmArgs& g, cudaStream_t s) {
     if (g.K <= 0 || !g.A || !g.B || !g.C) { set_error("gemm: bad arguments (M %d N %d K %d)", g.M, g.N, g.K); return WF_ERR_INVALID; }
     if (g_tc_min < 0) { const char* e = getenv("WF_SEQ_TC_MIN"); g_tc_min = e ? atoi(e) : 17; }
     if (g_force_simt < 0) { const char* e = getenv("WF_SEQ_GEMM_SIMT"); g_force_simt = (e && atoi(e)) ? 1 : 0; }
-    if (g.M <= 8 && g.batch == 1 && !g.tile_group && !g.a_rows) {      // decoding: stream the weights once
+    const bool few = g.batch == 1 && !g.tile_group && !g.a_rows && g.M <= 8;
+    if ((g.algo == 0 && few) || g.algo == 4) {      // decoding: stream the weights once
         const PairArgs none{nullptr, 0, 1};
-        if (dt == WF_F32 && gemv_ok<float>(g)) { gemv_launch<float>(g, none, g.M, 1, s); return launch_check(cudaGetLastError(), "gemv_rows"); }
-        if (dt == WF_BF16 && gemv_ok<__nv_bfloat16>(g)) { gemv_launch<__nv_bfloat16>(g, none, g.M, 1, s); return launch_check(cudaGetLastError(), "gemv_rows"); }
+        if (few && dt == WF_F32 && gemv_ok<float>(g)) { gemv_launch<float>(g, none, g.M, 1, s); return launch_check(cudaGetLastError(), "gemv_rows"); }
+        if (few && dt == WF_BF16 && gemv_ok<__nv_bfloat16>(g)) { gemv_launch<__nv_bfloat16>(g, none, g.M, 1, s); return launch_check(cudaGetLastError(), "gemv_rows"); }
+        if (g.algo == 4) { set_error("gemm: the few-row form does not take this shape"); return WF_ERR_UNSUPPORTED; }
     }
     dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, g.batch);
     if (grid.y > 65535u || grid.z > 65535u) { set_error("gemm: grid too large"); return WF_ERR_UNSUPPORTED; }
+    if (g.algo == 3 && (dt != WF_BF16 || !gemm_tc_usable(g))) { set_error("gemm: the tcgen05 form does not take this shape"); return WF_ERR_UNSUPPORTED; }
     if (dt == WF_F32) simt_dispatch<float>(g, grid, s);
-    else if (g_force_simt) simt_dispatch<__nv_bfloat16>(g, grid, s);
-    else if (g.M >= g_tc_min && gemm_tc_usable(g)) return launch_gemm_tc(g, g.n_groups, s);
+    else if (g.algo == 1 || (g.algo == 0 && g_force_simt)) simt_dispatch<__nv_bfloat16>(g, grid, s);
+    else if (g.algo == 3 || (g.algo == 0 && g.M >= g_tc_min && gemm_tc_usable(g))) return launch_gemm_tc(g, g.n_groups, s);
     else {
         if (g.a_f32) { if (g.c_f32) gemm_mma_kernel<true, true><<<grid, 128, 0, s>>>(g); else gemm_mma_kernel<true, false><<<grid, 128, 0, s>>>(g); }
         else { if (g.c_f32) gemm_mma_kernel<false, true><<<grid, 128, 0, s>>>(g); else gemm_mma_kernel<false, false><<<grid, 128, 0, s>>>(g); }

@@ -38,6 +38,7 @@ struct GemmArgs {
     long long group_stride = 0;
     const int32_t* a_rows = nullptr;
     int n_groups = 1;                        // weight matrices stacked behind B (grouped form)
+    int algo = 0;                            // 0 = choose; 1 plain FMA, 2 mma.sync, 3 tcgen05, 4 few-row streaming (tests and measurements)
 };
 constexpr int GEMM_BM = 128;                 // row granule of the grouped form (the token tile of the tcgen05 kernel)
 int launch_gemm(int dt, const GemmArgs& g, cudaStream_t s);
@@ -64,6 +65,12 @@ int launch_latent_kv_write(int dt, const Batch& b, const LatentDims& L, const fl
 // per (token, head): softmax over positions j in (pos - window, pos] of (qa . c_j + qr . kr_j) * scale; out T [n, H, R] = sum p_j c_j.
 // qa float [n, H, R] (the query carried through the key up-projection), qr float [n, H, r].
 int launch_latent_attn(int dt, const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, cudaStream_t s);
+// the same on tensor cores (bf16 storage only; seq_latent_mma.cu).  splits > 1 cuts every token's key range over that many CTAs and needs
+// workspace for n * splits partial results (latent_attn_mma_workspace(n * splits, H, R) bytes).  The cache rows must start 16-byte aligned.
+bool latent_attn_mma_usable(const LatentDims& L);
+size_t latent_attn_mma_workspace(int token_splits, int H, int R);
+int launch_latent_attn_mma(const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, float* workspace,
+                           int splits, cudaStream_t s);
 // y T [n, C] = x float [n, C] (ldx) * act(g float [n, C] (ldg)); act 0 = sigmoid, 1 = silu, 2 = none (a plain conversion of x)
 int launch_gate_mul(int dt, const float* x, int ldx, const float* g, int ldg, int act, int n, int C, void* y, int ldy, cudaStream_t s);
 // out T [H][C][R] = in T [H][R][C]   (per-head transpose, done once at load)

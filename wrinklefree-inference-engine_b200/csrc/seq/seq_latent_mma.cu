@@ -1,0 +1,268 @@
+// Latent attention on tensor cores (bf16 mma.sync, fp32 softmax): one CTA per (query token, key split) with ALL heads as the rows of
+// m16 tiles, because every head reads the same cached rows [latent c_j | rotated key part kr_j]:
+//   S[h, j] = (qa_h . c_j + qr_h . kr_j) * scale          Q = [qa | qr] rounded to bf16, K tile = 32 cached rows staged once for all heads
+//   O[h, :] = sum_j softmax_j(S[h, :]) c_j                 the same staged rows, read transposed, as the value operand
+// Four warps serve 16 heads: each computes the scores of 8 of the tile's 32 keys, the row maxima meet in shared memory, the
+// probabilities go to shared memory as bf16, and each warp accumulates a quarter of the latent dimensions.  Long windows with few
+// query tokens are split along the keys over several CTAs whose partial (max, sum, O) are merged by a second kernel.
+#include "seq_kernels.cuh"
+#include <math.h>
+
+namespace wf {
+namespace seq {
+
+namespace {
+
+constexpr int KT = 32;                    // keys per tile
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+struct MmaParams {
+    int splits;          // key splits per token (grid.y)
+    float* part;         // splits > 1: [n][splits][H][R + 2] partial (O unnormalised, max, sum)
+    int dkp;             // R + r rounded up to 16
+    int stride;          // shared-memory row stride of Q / K rows in elements (dkp + 8: conflict-free ldmatrix)
+};
+
+// NT = R / 32: n-tiles (8 latent dimensions each) per warp in the value product
+template <int NT>
+__global__ void latent_attn_mma_kernel(Batch b, LatentDims L, const float* __restrict__ qa, const float* __restrict__ qr, PagedCache pc,
+                                       __nv_bfloat16* __restrict__ out, MmaParams mp) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int HT = (L.H + 15) / 16, rows = HT * 16;
+    const int stride = mp.stride, width = L.R + L.r;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);                 // [rows][stride]
+    __nv_bfloat16* Ks = Qs + (size_t)rows * stride;                              // [2][KT][stride]
+    __nv_bfloat16* Ps = Ks + (size_t)2 * KT * stride;                            // [rows][KT + 8]
+    float* smax = reinterpret_cast<float*>(Ps + (size_t)rows * (KT + 8));        // [HT][4][16]
+    float* ssum = smax + HT * 64;                                                // [HT][4][16]
+    const int i = blockIdx.x, split = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ht = warp >> 2, w4 = warp & 3;                                     // head tile, warp inside it
+    const int sq = b.tok_seq[i], pos = b.tok_pos[i];
+    const int lo_all = pos - L.window + 1 > 0 ? pos - L.window + 1 : 0;
+    const int cnt = pos + 1 - lo_all;
+    int chunk = (cnt + mp.splits - 1) / mp.splits;
+    chunk = (chunk + KT - 1) / KT * KT;
+    const int lo = lo_all + split * chunk;
+    const int hi = lo + chunk < pos + 1 ? lo + chunk : pos + 1;                  // keys [lo, hi)
+    const int32_t* bt = pc.block_table + (size_t)b.seq_slot[sq] * pc.max_blocks;
+
+    // ---- Q = [qa | qr] of every head as bf16 (rows beyond H and columns beyond R + r are zero)
+    for (int idx = tid; idx < rows * mp.dkp; idx += blockDim.x) {
+        const int h = idx / mp.dkp, c = idx - h * mp.dkp;
+        float v = 0.f;
+        if (h < L.H) {
+            if (c < L.R) v = qa[((size_t)i * L.H + h) * L.R + c];
+            else if (c < width) v = qr[((size_t)i * L.H + h) * L.r + (c - L.R)];
+        }
+        Qs[(size_t)h * stride + c] = __float2bfloat16_rn(v);
+    }
+    // ---- staging of one key tile: 16-byte chunks of the cached rows; rows past `hi` and the padding columns are zero
+    const int chunks_per_row = mp.dkp / 8;
+    auto stage = [&](int buf, int j0) {
+        __nv_bfloat16* dst = Ks + (size_t)buf * KT * stride;
+        for (int idx = tid; idx < KT * chunks_per_row; idx += blockDim.x) {
+            const int kr_ = idx / chunks_per_row, c8 = (idx - kr_ * chunks_per_row) * 8;
+            const int j = j0 + kr_;
+            __nv_bfloat16* d = dst + (size_t)kr_ * stride + c8;
+            if (j < hi && c8 + 8 <= width) {
+                const int page = bt[j / pc.page_size];
+                const __nv_bfloat16* src = (const __nv_bfloat16*)pc.pool + (size_t)page * pc.page_stride + pc.layer_off + (size_t)(j % pc.page_size) * width + c8;
+                cp_async16(d, src);
+            } else {
+                *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        cp_async_commit();
+    };
+    float o[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};              // rows lane / 4 and lane / 4 + 8 of this head tile
+    const int r0 = lane >> 2, cq = (lane & 3) * 2;
+    const int ntiles = hi > lo ? (hi - lo + KT - 1) / KT : 0;
+    if (ntiles > 0) stage(0, lo);
+    for (int t = 0; t < ntiles; ++t) {
+        const int buf = t & 1;
+        cp_async_wait<0>();
+        __syncthreads();                                                          // tile t (and, first time, Q) visible; every warp is done with tile t - 1
+        if (t + 1 < ntiles) stage(buf ^ 1, lo + (t + 1) * KT);                    // overwrites the buffer tile t - 1 was read from
+        const __nv_bfloat16* Kt = Ks + (size_t)buf * KT * stride;
+        // ---- scores of this warp's 8 keys for the 16 heads of its tile
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        const __nv_bfloat16* qrow = Qs + (size_t)(ht * 16 + (lane & 15)) * stride + (lane >> 4) * 8;
+        const __nv_bfloat16* krow = Kt + (size_t)(w4 * 8 + (lane & 7)) * stride + ((lane >> 3) & 1) * 8;
+        for (int k0 = 0; k0 < mp.dkp; k0 += 16) {
+            uint32_t a[4], bb[2];
+            ldsm_x4(a, qrow + k0);
+            ldsm_x2(bb, krow + k0);
+            mma16816(s, a, bb[0], bb[1]);
+        }
+        const int jbase = lo + t * KT + w4 * 8 + cq;
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = jbase + (e & 1);
+            s[e] = j < hi ? s[e] * L.scale : -INFINITY;
+            tmax[e >> 1] = fmaxf(tmax[e >> 1], s[e]);
+        }
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            tmax[h2] = fmaxf(tmax[h2], __shfl_xor_sync(0xffffffffu, tmax[h2], 1));
+            tmax[h2] = fmaxf(tmax[h2], __shfl_xor_sync(0xffffffffu, tmax[h2], 2));
+        }
+        if ((lane & 3) == 0) { smax[(ht * 4 + w4) * 16 + r0] = tmax[0]; smax[(ht * 4 + w4) * 16 + r0 + 8] = tmax[1]; }
+        __syncthreads();
+        float corr[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            const int r = r0 + h2 * 8;
+            float mx = smax[(ht * 4 + 0) * 16 + r];
+            mx = fmaxf(mx, smax[(ht * 4 + 1) * 16 + r]);
+            mx = fmaxf(mx, smax[(ht * 4 + 2) * 16 + r]);
+            mx = fmaxf(mx, smax[(ht * 4 + 3) * 16 + r]);
+            const float mn = fmaxf(m_run[h2], mx);                                // finite: key lo + t * KT exists in every tile
+            corr[h2] = expf(m_run[h2] - mn);
+            m_run[h2] = mn;
+            const float p0 = expf(s[h2 * 2] - mn), p1 = expf(s[h2 * 2 + 1] - mn);
+            l_run[h2] = l_run[h2] * corr[h2] + p0 + p1;
+            __nv_bfloat162 pv = __floats2bfloat162_rn(p0, p1);
+            *reinterpret_cast<__nv_bfloat162*>(Ps + (size_t)(ht * 16 + r) * (KT + 8) + w4 * 8 + cq) = pv;
+        }
+        __syncthreads();
+        // ---- O[16 heads, this warp's quarter of the latent] = O * corr + P[16, 32] . C[32, quarter]
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) { o[nt][0] *= corr[0]; o[nt][1] *= corr[0]; o[nt][2] *= corr[1]; o[nt][3] *= corr[1]; }
+        const __nv_bfloat16* prow = Ps + (size_t)(ht * 16 + (lane & 15)) * (KT + 8) + (lane >> 4) * 8;
+        const int ncol0 = w4 * NT * 8;
+#pragma unroll
+        for (int k0 = 0; k0 < KT; k0 += 16) {
+            uint32_t a[4];
+            ldsm_x4(a, prow + k0);
+            const __nv_bfloat16* crow = Kt + (size_t)(k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * stride + ncol0 + (lane >> 4) * 8;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt += 2) {
+                uint32_t bb[4];
+                ldsm_x4_trans(bb, crow + nt * 8);
+                mma16816(o[nt], a, bb[0], bb[1]);
+                if (nt + 1 < NT) mma16816(o[nt + 1], a, bb[2], bb[3]);
+            }
+        }
+    }
+    // ---- row sums of the four warps meet; normalise (or hand the partial result to the merge)
+    __syncthreads();
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+        l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 1);
+        l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 2);
+    }
+    if ((lane & 3) == 0) { ssum[(ht * 4 + w4) * 16 + r0] = l_run[0]; ssum[(ht * 4 + w4) * 16 + r0 + 8] = l_run[1]; }
+    __syncthreads();
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+        const int r = r0 + h2 * 8, h = ht * 16 + r;
+        if (h >= L.H) continue;
+        const float lsum = ssum[(ht * 4 + 0) * 16 + r] + ssum[(ht * 4 + 1) * 16 + r] + ssum[(ht * 4 + 2) * 16 + r] + ssum[(ht * 4 + 3) * 16 + r];
+        if (mp.splits == 1) {
+            const float inv = 1.f / lsum;
+            __nv_bfloat16* dst = out + ((size_t)i * L.H + h) * L.R + w4 * NT * 8 + cq;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+                *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) = __floats2bfloat162_rn(o[nt][h2 * 2] * inv, o[nt][h2 * 2 + 1] * inv);
+        } else {
+            float* dst = mp.part + (((size_t)i * mp.splits + split) * L.H + h) * (L.R + 2);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) { dst[w4 * NT * 8 + cq + nt * 8] = o[nt][h2 * 2]; dst[w4 * NT * 8 + cq + nt * 8 + 1] = o[nt][h2 * 2 + 1]; }
+            if (w4 == 0 && (lane & 3) == 0) { dst[L.R] = m_run[h2]; dst[L.R + 1] = lsum; }
+        }
+    }
+}
+
+// one block per (token, head): out = sum_s exp(m_s - m) O_s / sum_s exp(m_s - m) l_s
+__global__ void latent_attn_merge_kernel(int H, int R, int splits, const float* __restrict__ part, __nv_bfloat16* __restrict__ out) {
+    const int i = blockIdx.x, h = blockIdx.y;
+    const float* p0 = part + (((size_t)i * splits) * H + h) * (R + 2);
+    const size_t sstride = (size_t)H * (R + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, p0[s * sstride + R]);
+    float l = 0.f;
+    for (int s = 0; s < splits; ++s) { const float ms = p0[s * sstride + R]; if (ms != -INFINITY) l += expf(ms - m) * p0[s * sstride + R + 1]; }
+    const float inv = 1.f / l;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < splits; ++s) { const float ms = p0[s * sstride + R]; if (ms != -INFINITY) v += expf(ms - m) * p0[s * sstride + c]; }
+        out[((size_t)i * H + h) * R + c] = __float2bfloat16_rn(v * inv);
+    }
+}
+
+template <int NT>
+int launch_nt(const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, const MmaParams& mp, size_t smem,
+              cudaStream_t s) {
+    static DevOnce once;
+    if (once.need()) cudaFuncSetAttribute(latent_attn_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    const int HT = (L.H + 15) / 16;
+    dim3 grid(b.n, mp.splits);
+    latent_attn_mma_kernel<NT><<<grid, HT * 128, smem, s>>>(b, L, qa, qr, pc, (__nv_bfloat16*)out, mp);
+    return launch_check(cudaGetLastError(), "latent_attn_mma");
+}
+
+}  // namespace
+
+size_t latent_attn_mma_workspace(int token_splits, int H, int R) { return (size_t)token_splits * H * (R + 2) * sizeof(float); }
+
+bool latent_attn_mma_usable(const LatentDims& L) {
+    if (L.R % 32 || (L.R + L.r) % 8 || L.H > 128) return false;
+    const int nt = L.R / 32;
+    if (!(nt == 1 || nt == 2 || nt == 3 || nt == 4 || nt == 6 || nt == 8 || nt == 12 || nt == 16)) return false;
+    const int HT = (L.H + 15) / 16, dkp = (L.R + L.r + 15) / 16 * 16, stride = dkp + 8;
+    const size_t smem = ((size_t)HT * 16 * stride + 2 * KT * stride + (size_t)HT * 16 * (KT + 8)) * 2 + (size_t)HT * 128 * 4;
+    return smem <= 200 * 1024 && HT * 128 <= 1024;
+}
+
+int launch_latent_attn_mma(const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, float* workspace,
+                           int splits, cudaStream_t s) {
+    if (b.n <= 0) return WF_OK;
+    MmaParams mp;
+    mp.splits = splits < 1 ? 1 : (splits > 16 ? 16 : splits);
+    mp.part = workspace;
+    mp.dkp = (L.R + L.r + 15) / 16 * 16;
+    mp.stride = mp.dkp + 8;
+    if (mp.splits > 1 && !workspace) mp.splits = 1;
+    const int HT = (L.H + 15) / 16;
+    const size_t smem = ((size_t)HT * 16 * mp.stride + 2 * KT * mp.stride + (size_t)HT * 16 * (KT + 8)) * 2 + (size_t)HT * 128 * 4;
+    int rc;
+    switch (L.R / 32) {
+        case 1: rc = launch_nt<1>(b, L, qa, qr, pc, out, mp, smem, s); break;
+        case 2: rc = launch_nt<2>(b, L, qa, qr, pc, out, mp, smem, s); break;
+        case 3: rc = launch_nt<3>(b, L, qa, qr, pc, out, mp, smem, s); break;
+        case 4: rc = launch_nt<4>(b, L, qa, qr, pc, out, mp, smem, s); break;
+        case 6: rc = launch_nt<6>(b, L, qa, qr, pc, out, mp, smem, s); break;
+        case 8: rc = launch_nt<8>(b, L, qa, qr, pc, out, mp, smem, s); break;
+        case 12: rc = launch_nt<12>(b, L, qa, qr, pc, out, mp, smem, s); break;
+        case 16: rc = launch_nt<16>(b, L, qa, qr, pc, out, mp, smem, s); break;
+        default: set_error("latent_attn_mma: unsupported latent size %d", L.R); return WF_ERR_UNSUPPORTED;
+    }
+    if (rc) return rc;
+    if (mp.splits > 1) {
+        dim3 grid(b.n, L.H);
+        latent_attn_merge_kernel<<<grid, 128, 0, s>>>(L.H, L.R, mp.splits, workspace, (__nv_bfloat16*)out);
+        return launch_check(cudaGetLastError(), "latent_attn_merge");
+    }
+    return WF_OK;
+}
+
+}  // namespace seq
+}  // namespace wf

@@ -159,6 +159,7 @@ SEQ_SYMBOLS = {
     "wf_seq_time_step": (_i, [_vp, _i, _vp, _vp, _i, _fp]),
     "wf_seq_profile_step": (_i, [_vp, _i, _vp, _vp, _i, C.c_char_p, _sz]),
     "wf_seq_set_length": (_i, [_vp, _i, _i]),
+    "wf_seq_op_gemm": (_i, [_i, _vp, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, C.c_longlong, _i, _i, _vp]),
 }
 _seq_lib = None
 
