@@ -113,7 +113,7 @@ __global__ void delta_post_kernel(DeltaDims D, const float* __restrict__ o, cons
                                   T* __restrict__ y) {
     const int i = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int h = warp; h < D.H; h += nw) {
+    for (int h = blockIdx.y * nw + warp; h < D.H; h += gridDim.y * nw) {
         const float* x = o + ((size_t)i * D.H + h) * D.dv;
         float ss = 0.f;
         for (int c = lane; c < D.dv; c += 32) ss += x[c] * x[c];
@@ -153,8 +153,9 @@ int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int 
 
 int launch_delta_post(int dt, const DeltaDims& D, int n, const float* o, const void* w, float eps, const float* g, int ldg, void* y, cudaStream_t s) {
     if (n <= 0) return WF_OK;
-    if (dt == WF_BF16) delta_post_kernel<<<n, 128, 0, s>>>(D, o, (const __nv_bfloat16*)w, eps, g, ldg, (__nv_bfloat16*)y);
-    else delta_post_kernel<<<n, 128, 0, s>>>(D, o, (const float*)w, eps, g, ldg, (float*)y);
+    const dim3 grid(n, n < 64 ? (D.H + 3) / 4 : 1);
+    if (dt == WF_BF16) delta_post_kernel<<<grid, 128, 0, s>>>(D, o, (const __nv_bfloat16*)w, eps, g, ldg, (__nv_bfloat16*)y);
+    else delta_post_kernel<<<grid, 128, 0, s>>>(D, o, (const float*)w, eps, g, ldg, (float*)y);
     return launch_check(cudaGetLastError(), "delta_post");
 }
 

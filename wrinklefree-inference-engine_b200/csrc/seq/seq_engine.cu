@@ -72,6 +72,7 @@ struct wf_seq_engine {
     void *hperm = nullptr, *h_t = nullptr, *qn = nullptr, *olat = nullptr, *og = nullptr, *hmid = nullptr, *xn = nullptr;
     int32_t *ids = nullptr, *counts = nullptr, *plan_scratch = nullptr, *sorted_rows = nullptr, *pair_row = nullptr, *tile_group = nullptr;
     int P = 0;                        // padded expert-row bound
+    int fuse_input = 1;               // norm + input convolution (+ state roll of single-token sequences) in one kernel (WF_SEQ_FUSE_INPUT=0: three kernels)
     int attn_mma = 1;                 // latent attention on tensor cores where the sizes allow it (WF_SEQ_ATTN_MMA=0: the plain kernel)
     float* attn_ws = nullptr;         // partial results of key-split attention
     int attn_ws_rows = 0;             // token-splits it holds
@@ -82,6 +83,11 @@ struct wf_seq_engine {
     int32_t* d_next = nullptr;
     size_t sample_rows = 0;
     float* layer_tap = nullptr;
+    // decode-only steps (one token per sequence) replay a CUDA graph captured per (sequences, wanted rows): their launch parameters depend
+    // on nothing else.  A shape runs eagerly the first time (one-time kernel attributes are set then) and is captured the second time.
+    int graph_max = 64;               // WF_SEQ_GRAPH_MAX: largest decode batch that is graphed (0: never)
+    std::map<std::pair<int, int>, cudaGraphExec_t> graphs;
+    std::map<std::pair<int, int>, int> graph_seen;
     // per-kernel-kind timing (wf_seq_profile_step): an event after every launch group; the time since the previous event goes to its label
     bool prof = false;
     std::vector<std::pair<const char*, cudaEvent_t>> marks;
@@ -238,10 +244,12 @@ int run_latent(wf_seq_engine* e, LayerState& L, const Batch& b) {
     }
     if (e->dt == WF_BF16 && e->attn_mma && latent_attn_mma_usable(D) && L.cache_off % 8 == 0 && e->page_stride % 8 == 0) {
         // few query tokens and a long window: split the keys so that the machine is busy
+        // (a CTA holds Q, two key tiles and P in shared memory: that decides how many are resident at once)
         int splits = 1;
         const int span = c.window < e->cfg.max_pages * e->cfg.page_size ? c.window : e->cfg.max_pages * e->cfg.page_size;
-        if (n < 2 * sm_count()) {
-            splits = (2 * sm_count() + n - 1) / n;
+        const int resident = sm_count() * latent_attn_mma_ctas_per_sm(D);
+        if (2 * n <= resident) {
+            splits = resident / n;                               // one full wave, no second partial one
             if (splits > span / 128) splits = span / 128;
             if (splits > e->attn_ws_rows / n) splits = e->attn_ws_rows / n;
             if (splits > 16) splits = 16;
@@ -347,9 +355,15 @@ int run_input(wf_seq_engine* e, const Batch& b, const void* norm_w, const void* 
     const int W = e->cfg.width;
     cudaStream_t s = e->stream;
     int rc;
-    if ((rc = launch_group_rmsnorm(e->dt, e->x, W, norm_w, e->cfg.norm_groups, e->cfg.eps, b.n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s))) return rc;
-    if ((rc = launch_causal_taps(e->dt, b, e->hn, W, canon_w, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, 1, 0, e->h_t, W, nullptr, 0, s))) return rc;
-    rc = launch_taps_state(b, e->hn, W, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, s);
+    if (e->fuse_input && norm_taps_usable(e->cfg.norm_groups, e->cfg.canon_taps, W)) {
+        if ((rc = launch_norm_taps(e->dt, b, e->x, W, norm_w, e->cfg.norm_groups, e->cfg.eps, canon_w, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride,
+                                   e->h_t, W, e->hn, s))) return rc;
+        rc = b.n == b.nseq ? WF_OK : launch_taps_state(b, e->hn, W, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, s, 1);
+    } else {
+        if ((rc = launch_group_rmsnorm(e->dt, e->x, W, norm_w, e->cfg.norm_groups, e->cfg.eps, b.n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s))) return rc;
+        if ((rc = launch_causal_taps(e->dt, b, e->hn, W, canon_w, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, 1, 0, e->h_t, W, nullptr, 0, s))) return rc;
+        rc = launch_taps_state(b, e->hn, W, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, s);
+    }
     mark(e, "norm+input_conv");
     return rc;
 }
@@ -381,6 +395,8 @@ int run_layers(wf_seq_engine* e, const StepView& v) {
 
 int ensure_logits(wf_seq_engine* e, size_t rows) {
     if (rows <= e->logits_rows) return WF_OK;
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);      // captured steps hold the old buffer's address
+    e->graphs.clear();
     if (e->logits) { cudaFree(e->logits); e->dev_bytes -= e->logits_rows * e->cfg.vocab * 4; }
     e->logits = nullptr; e->logits_rows = 0;
     if (cuda_check(cudaMalloc((void**)&e->logits, rows * e->cfg.vocab * 4), "cudaMalloc logits")) return WF_ERR_CUDA;
@@ -398,6 +414,38 @@ int run_head(wf_seq_engine* e, const StepView& v, int nwant) {
     rc = launch_gemm(e->dt, lin(e->xn, 0, W, e->head, W, e->logits, 1, e->cfg.vocab, nwant, e->cfg.vocab, W), e->stream);
     mark(e, "final_norm+head_gemm");
     return rc;
+}
+
+// layers + head of one step: eagerly, or (decode-only shapes seen before) as a captured graph
+int run_model(wf_seq_engine* e, const StepView& v, int nwant) {
+    int rc;
+    const bool decode_only = v.b.n == v.b.nseq;
+    if (!decode_only || v.b.n > e->graph_max || e->layer_tap || e->prof) {
+        if ((rc = run_layers(e, v))) return rc;
+        return run_head(e, v, nwant);
+    }
+    if ((rc = ensure_logits(e, nwant))) return rc;
+    const std::pair<int, int> key(v.b.n, nwant);
+    auto it = e->graphs.find(key);
+    if (it == e->graphs.end()) {
+        if (e->graph_seen[key]++ == 0) {
+            if ((rc = run_layers(e, v))) return rc;
+            return run_head(e, v, nwant);
+        }
+        if (cuda_check(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal), "begin capture")) return WF_ERR_CUDA;
+        rc = run_layers(e, v);
+        if (!rc) rc = run_head(e, v, nwant);
+        cudaGraph_t graph = nullptr;
+        const cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+        if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+        if (cuda_check(ce, "end capture")) return WF_ERR_CUDA;
+        cudaGraphExec_t exec = nullptr;
+        const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (cuda_check(ie, "graph instantiate")) return WF_ERR_CUDA;
+        it = e->graphs.emplace(key, exec).first;
+    }
+    return cuda_check(cudaGraphLaunch(it->second, e->stream), "graph launch");
 }
 
 }  // namespace
@@ -421,6 +469,8 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     e->esz = e->dt == WF_F32 ? 4 : 2;
     if (const char* pm = getenv("WF_SEQ_PAIR_MAX")) e->pair_path_max = atoi(pm);
     if (const char* am = getenv("WF_SEQ_ATTN_MMA")) e->attn_mma = atoi(am);
+    if (const char* gm = getenv("WF_SEQ_GRAPH_MAX")) e->graph_max = atoi(gm);
+    if (const char* fi = getenv("WF_SEQ_FUSE_INPUT")) e->fuse_input = atoi(fi);
     const wf_seq_config& c = e->cfg;
     const int W = c.width, T = c.max_step_tokens, taps = c.canon_taps;
     int rc = WF_OK;
@@ -550,6 +600,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
 extern "C" void wf_seq_destroy(wf_seq_engine* e) {
     if (!e) return;
     if (e->stream) cudaStreamSynchronize(e->stream);
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
     for (void* p : e->allocs) cudaFree(p);
     if (e->logits) cudaFree(e->logits);
     if (e->d_uniform) cudaFree(e->d_uniform);
@@ -625,9 +676,8 @@ extern "C" int wf_seq_step(wf_seq_engine* e, int nseq, const int32_t* slots, con
     int rc;
     if ((rc = prepare_step(e, nseq, slots, counts, tokens, nwant, want, &v))) return rc;
     const long long l0 = launch_count();
-    if ((rc = run_layers(e, v))) return rc;
-    if ((rc = run_head(e, v, nwant))) return rc;
-    e->launches = (int)(launch_count() - l0);
+    if ((rc = run_model(e, v, nwant))) return rc;
+    if (launch_count() > l0) e->launches = (int)(launch_count() - l0);     // a graph replay launches what its capture counted
     if (logits_host && nwant > 0)
         if (cuda_check(cudaMemcpyAsync(logits_host, e->logits, (size_t)nwant * e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream), "logits D2H")) return WF_ERR_CUDA;
     if (cuda_check(cudaStreamSynchronize(e->stream), "wf_seq_step")) return WF_ERR_CUDA;
@@ -710,7 +760,7 @@ extern "C" int wf_seq_profile_step(wf_seq_engine* e, int nseq, const int32_t* sl
     e->prof = false;
     std::map<std::string, std::pair<double, int>> acc;
     if (!rc) {
-        // the first (untimed) pass of wf_seq_time_step is included: iters + 1 passes
+        // the untimed passes of wf_seq_time_step are included: iters + 2 passes
         for (size_t i = 1; i < e->marks.size(); ++i) {
             float t = 0.f;
             cudaEventElapsedTime(&t, e->marks[i - 1].second, e->marks[i].second);
@@ -724,7 +774,7 @@ extern "C" int wf_seq_profile_step(wf_seq_engine* e, int nseq, const int32_t* sl
     std::string js = "{";
     char buf[160];
     for (auto& kv : acc) {
-        snprintf(buf, sizeof buf, "%s\"%s\": [%.6f, %d]", js.size() > 1 ? ", " : "", kv.first.c_str(), kv.second.first / (iters + 1), kv.second.second / (iters + 1));
+        snprintf(buf, sizeof buf, "%s\"%s\": [%.6f, %d]", js.size() > 1 ? ", " : "", kv.first.c_str(), kv.second.first / (iters + 2), kv.second.second / (iters + 2));
         js += buf;
     }
     js += "}";
@@ -747,9 +797,9 @@ extern "C" int wf_seq_time_step(wf_seq_engine* e, int nseq, const int32_t* slots
     if ((rc = prepare_step(e, nseq, slots, counts, tokens.data(), nseq, want.data(), &v))) return rc;
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0); cudaEventCreate(&e1);
-    for (int it = -1; it < iters; ++it) {      // one untimed pass first
+    for (int it = -2; it < iters; ++it) {      // two untimed passes first (the second one captures the graph of a decode shape)
         if (it == 0) cudaEventRecord(e0, e->stream);
-        if ((rc = run_layers(e, v)) || (rc = run_head(e, v, nseq))) break;
+        if ((rc = run_model(e, v, nseq))) break;
     }
     cudaEventRecord(e1, e->stream);
     const cudaError_t ce = cudaStreamSynchronize(e->stream);

@@ -20,7 +20,13 @@ int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int gro
 // read here and rolled forward by launch_taps_state AFTER this kernel.  out: T [n, C] (out_t) and / or float (out_f).
 int launch_causal_taps(int dt, const Batch& b, const float* in, int ld_in, const void* w, int taps, int C, const float* state,
                        size_t slot_stride, int identity, int silu, void* out_t, int ld_t, float* out_f, int ld_f, cudaStream_t s);
-int launch_taps_state(const Batch& b, const float* in, int ld_in, int taps, int C, float* state, size_t slot_stride, cudaStream_t s);
+int launch_taps_state(const Batch& b, const float* in, int ld_in, int taps, int C, float* state, size_t slot_stride, cudaStream_t s, int skip_single = 0);
+// grouped RMS norm of x (float [n, W]) and the identity-plus-taps convolution over the normalised rows in one kernel: out_t T [n, W].
+// hn (float [n, W]) receives the normalised rows of each portion's last taps - 1 tokens, for launch_taps_state(..., skip_single = 1)
+// afterwards; sequences that bring one token have their state rolled here.
+inline bool norm_taps_usable(int groups, int taps, int W) { return groups >= 1 && groups <= 32 && taps >= 1 && taps <= 8 && W % groups == 0; }
+int launch_norm_taps(int dt, const Batch& b, const float* x, int ldx, const void* nw, int groups, float eps, const void* cw, int taps, int W, float* state,
+                     size_t slot_stride, void* out_t, int ld_t, float* hn, cudaStream_t s);
 
 // C[m, n] = sum_k A[m, k] * B[n, k]  (B stored [N, K] row-major, i.e. a Linear weight), float accumulation.
 struct GemmArgs {
@@ -69,6 +75,7 @@ int launch_latent_attn(int dt, const Batch& b, const LatentDims& L, const float*
 // workspace for n * splits partial results (latent_attn_mma_workspace(n * splits, H, R) bytes).  The cache rows must start 16-byte aligned.
 bool latent_attn_mma_usable(const LatentDims& L);
 size_t latent_attn_mma_workspace(int token_splits, int H, int R);
+int latent_attn_mma_ctas_per_sm(const LatentDims& L);   // resident CTAs per SM (shared-memory bound)
 int launch_latent_attn_mma(const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, float* workspace,
                            int splits, cudaStream_t s);
 // y T [n, C] = x float [n, C] (ldx) * act(g float [n, C] (ldg)); act 0 = sigmoid, 1 = silu, 2 = none (a plain conversion of x)

@@ -26,7 +26,7 @@ __global__ void latent_q_prep_kernel(Batch b, LatentDims L, const float* __restr
     const int i = blockIdx.x;
     const int pos = b.tok_pos[i];
     const int per = L.d + L.r, half = L.rope_dims / 2;
-    for (int idx = threadIdx.x; idx < L.H * per; idx += blockDim.x) {
+    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < L.H * per; idx += gridDim.y * blockDim.x) {
         const int h = idx / per, c = idx % per;
         const float* src = q + (size_t)i * ldq + (size_t)h * per;
         if (c < L.d) { qn[((size_t)i * L.H + h) * L.d + c] = from_f<T>(src[c]); continue; }
@@ -151,8 +151,9 @@ int check_dims(const LatentDims& L) {
 int launch_latent_q_prep(int dt, const Batch& b, const LatentDims& L, const float* q, int ldq, void* qn, float* qr, cudaStream_t s) {
     if (b.n <= 0) return WF_OK;
     if (int rc = check_dims(L)) return rc;
-    if (dt == WF_BF16) latent_q_prep_kernel<<<b.n, 256, 0, s>>>(b, L, q, ldq, (__nv_bfloat16*)qn, qr);
-    else latent_q_prep_kernel<<<b.n, 256, 0, s>>>(b, L, q, ldq, (float*)qn, qr);
+    const dim3 grid(b.n, b.n < 64 ? (L.H * (L.d + L.r) + 255) / 256 : 1);
+    if (dt == WF_BF16) latent_q_prep_kernel<<<grid, 256, 0, s>>>(b, L, q, ldq, (__nv_bfloat16*)qn, qr);
+    else latent_q_prep_kernel<<<grid, 256, 0, s>>>(b, L, q, ldq, (float*)qn, qr);
     return launch_check(cudaGetLastError(), "latent_q_prep");
 }
 

@@ -60,31 +60,38 @@ __global__ void latent_attn_mma_kernel(Batch b, LatentDims L, const float* __res
     const int hi = lo + chunk < pos + 1 ? lo + chunk : pos + 1;                  // keys [lo, hi)
     const int32_t* bt = pc.block_table + (size_t)b.seq_slot[sq] * pc.max_blocks;
 
-    // ---- Q = [qa | qr] of every head as bf16 (rows beyond H and columns beyond R + r are zero)
-    for (int idx = tid; idx < rows * mp.dkp; idx += blockDim.x) {
-        const int h = idx / mp.dkp, c = idx - h * mp.dkp;
-        float v = 0.f;
-        if (h < L.H) {
-            if (c < L.R) v = qa[((size_t)i * L.H + h) * L.R + c];
-            else if (c < width) v = qr[((size_t)i * L.H + h) * L.r + (c - L.R)];
-        }
-        Qs[(size_t)h * stride + c] = __float2bfloat16_rn(v);
-    }
-    // ---- staging of one key tile: 16-byte chunks of the cached rows; rows past `hi` and the padding columns are zero
-    const int chunks_per_row = mp.dkp / 8;
-    auto stage = [&](int buf, int j0) {
-        __nv_bfloat16* dst = Ks + (size_t)buf * KT * stride;
-        for (int idx = tid; idx < KT * chunks_per_row; idx += blockDim.x) {
-            const int kr_ = idx / chunks_per_row, c8 = (idx - kr_ * chunks_per_row) * 8;
-            const int j = j0 + kr_;
-            __nv_bfloat16* d = dst + (size_t)kr_ * stride + c8;
-            if (j < hi && c8 + 8 <= width) {
-                const int page = bt[j / pc.page_size];
-                const __nv_bfloat16* src = (const __nv_bfloat16*)pc.pool + (size_t)page * pc.page_stride + pc.layer_off + (size_t)(j % pc.page_size) * width + c8;
-                cp_async16(d, src);
-            } else {
-                *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+    // ---- Q = [qa | qr] of every head as bf16 (rows beyond H and columns beyond R + r are zero): a warp per head, lanes over columns
+    const int nwarps = blockDim.x >> 5;
+    for (int h = warp; h < rows; h += nwarps) {
+        __nv_bfloat16* qd = Qs + (size_t)h * stride;
+        const float* a_src = qa + ((size_t)i * L.H + h) * L.R;
+        const float* r_src = qr + ((size_t)i * L.H + h) * L.r;
+        for (int c = lane; c < mp.dkp; c += 32) {
+            float v = 0.f;
+            if (h < L.H) {
+                if (c < L.R) v = a_src[c];
+                else if (c < width) v = r_src[c - L.R];
             }
+            qd[c] = __float2bfloat16_rn(v);
+        }
+    }
+    // ---- staging of one key tile: 16-byte chunks of the cached rows; rows past `hi` and the padding columns are zero.
+    // A thread always serves the same row of the tile (one page lookup per tile) and every tpr-th chunk of it.
+    const int chunks_per_row = mp.dkp / 8;
+    const int tpr = blockDim.x / KT;                                              // threads per key row (4 warps per 16 heads: >= 4)
+    const int st_row = tid / tpr, st_sub = tid - st_row * tpr;
+    auto stage = [&](int buf, int j0) {
+        __nv_bfloat16* d = Ks + ((size_t)buf * KT + st_row) * stride;
+        const int j = j0 + st_row;
+        if (j < hi) {
+            const int page = bt[j / pc.page_size];
+            const __nv_bfloat16* src = (const __nv_bfloat16*)pc.pool + (size_t)page * pc.page_stride + pc.layer_off + (size_t)(j % pc.page_size) * width;
+            for (int c = st_sub; c < chunks_per_row; c += tpr) {
+                if (c * 8 + 8 <= width) cp_async16(d + c * 8, src + c * 8);
+                else *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        } else {
+            for (int c = st_sub; c < chunks_per_row; c += tpr) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0u, 0u, 0u, 0u);
         }
         cp_async_commit();
     };
@@ -102,15 +109,30 @@ __global__ void latent_attn_mma_kernel(Batch b, LatentDims L, const float* __res
         if (t + 1 < ntiles) stage(buf ^ 1, lo + (t + 1) * KT);                    // overwrites the buffer tile t - 1 was read from
         const __nv_bfloat16* Kt = Ks + (size_t)buf * KT * stride;
         // ---- scores of this warp's 8 keys for the 16 heads of its tile
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        // (four independent accumulation chains over the feature dimension, summed at the end: one chain would be latency-bound)
+        float s[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f}, s3[4] = {0.f, 0.f, 0.f, 0.f};
         const __nv_bfloat16* qrow = Qs + (size_t)(ht * 16 + (lane & 15)) * stride + (lane >> 4) * 8;
         const __nv_bfloat16* krow = Kt + (size_t)(w4 * 8 + (lane & 7)) * stride + ((lane >> 3) & 1) * 8;
-        for (int k0 = 0; k0 < mp.dkp; k0 += 16) {
+        int k0 = 0;
+        for (; k0 + 64 <= mp.dkp; k0 += 64) {
+            uint32_t a0[4], a1[4], a2[4], a3[4], b0[2], b1[2], b2[2], b3[2];
+            ldsm_x4(a0, qrow + k0); ldsm_x2(b0, krow + k0);
+            ldsm_x4(a1, qrow + k0 + 16); ldsm_x2(b1, krow + k0 + 16);
+            ldsm_x4(a2, qrow + k0 + 32); ldsm_x2(b2, krow + k0 + 32);
+            ldsm_x4(a3, qrow + k0 + 48); ldsm_x2(b3, krow + k0 + 48);
+            mma16816(s, a0, b0[0], b0[1]);
+            mma16816(s1, a1, b1[0], b1[1]);
+            mma16816(s2, a2, b2[0], b2[1]);
+            mma16816(s3, a3, b3[0], b3[1]);
+        }
+        for (; k0 < mp.dkp; k0 += 16) {
             uint32_t a[4], bb[2];
             ldsm_x4(a, qrow + k0);
             ldsm_x2(bb, krow + k0);
             mma16816(s, a, bb[0], bb[1]);
         }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] += s1[e] + s2[e] + s3[e];
         const int jbase = lo + t * KT + w4 * 8 + cq;
         float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -222,6 +244,15 @@ int launch_nt(const Batch& b, const LatentDims& L, const float* qa, const float*
 }  // namespace
 
 size_t latent_attn_mma_workspace(int token_splits, int H, int R) { return (size_t)token_splits * H * (R + 2) * sizeof(float); }
+
+int latent_attn_mma_ctas_per_sm(const LatentDims& L) {
+    const int HT = (L.H + 15) / 16, dkp = (L.R + L.r + 15) / 16 * 16, stride = dkp + 8;
+    const size_t smem = ((size_t)HT * 16 * stride + 2 * KT * stride + (size_t)HT * 16 * (KT + 8)) * 2 + (size_t)HT * 128 * 4 + 1024;
+    int k = (int)((227 * 1024) / smem);
+    const int by_threads = 2048 / (HT * 128);
+    if (k > by_threads) k = by_threads;
+    return k < 1 ? 1 : k;
+}
 
 bool latent_attn_mma_usable(const LatentDims& L) {
     if (L.R % 32 || (L.R + L.r) % 8 || L.H > 128) return false;

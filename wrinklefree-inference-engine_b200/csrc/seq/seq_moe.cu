@@ -100,14 +100,14 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, int ff, const int3
     const int r = blockIdx.x;
     if (tile_group && tile_group[r / GEMM_BM] < 0) return;
     const float* row = gu + (size_t)r * 2 * ff;
-    for (int c = threadIdx.x; c < ff; c += blockDim.x) hmid[(size_t)r * ff + c] = from_f<T>(silu_f(row[c]) * row[ff + c]);
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ff; c += gridDim.y * blockDim.x) hmid[(size_t)r * ff + c] = from_f<T>(silu_f(row[c]) * row[ff + c]);
 }
 
 template <typename T>
 __global__ void moe_combine_kernel(RouterDims R, int W, const int32_t* __restrict__ ids, const float* __restrict__ wts, const int32_t* __restrict__ pair_row,
                                    const float* __restrict__ y, const T* __restrict__ h, float* __restrict__ out) {
     const int i = blockIdx.x;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < R.top; ++k) {
             const int e = ids[(size_t)i * R.top + k];
@@ -147,16 +147,18 @@ int launch_moe_plan(const RouterDims& R, int n, const int32_t* ids, const int32_
 
 int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s) {
     if (P <= 0) return WF_OK;
-    if (dt == WF_BF16) silu_mul_kernel<<<P, 128, 0, s>>>(gu, ff, tile_group, (__nv_bfloat16*)hmid);
-    else silu_mul_kernel<<<P, 128, 0, s>>>(gu, ff, tile_group, (float*)hmid);
+    const dim3 grid(P, P < 256 ? (ff + 127) / 128 : 1);
+    if (dt == WF_BF16) silu_mul_kernel<<<grid, 128, 0, s>>>(gu, ff, tile_group, (__nv_bfloat16*)hmid);
+    else silu_mul_kernel<<<grid, 128, 0, s>>>(gu, ff, tile_group, (float*)hmid);
     return launch_check(cudaGetLastError(), "silu_mul");
 }
 
 int launch_moe_combine(int dt, const RouterDims& R, int n, int W, const int32_t* ids, const float* wts, const int32_t* pair_row, const float* y,
                        const void* h, float* out, cudaStream_t s) {
     if (n <= 0) return WF_OK;
-    if (dt == WF_BF16) moe_combine_kernel<<<n, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const __nv_bfloat16*)h, out);
-    else moe_combine_kernel<<<n, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const float*)h, out);
+    const dim3 grid(n, n < 64 ? (W + 255) / 256 : 1);       // few tokens: spread a row over several blocks
+    if (dt == WF_BF16) moe_combine_kernel<<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const __nv_bfloat16*)h, out);
+    else moe_combine_kernel<<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const float*)h, out);
     return launch_check(cudaGetLastError(), "moe_combine");
 }
 

@@ -44,7 +44,7 @@ int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int gro
     if (groups <= 0 || W % groups) { set_error("group_rmsnorm: width %d not divisible into %d groups", W, groups); return WF_ERR_INVALID; }
     if (res && rows && y == res) { set_error("group_rmsnorm: gathered rows cannot be added in place"); return WF_ERR_INVALID; }
     const int gw = W / groups;
-    const int threads = gw >= 1024 ? 256 : (gw >= 256 ? 128 : 64);
+    const int threads = gw >= 2048 ? 512 : (gw >= 1024 ? 256 : (gw >= 256 ? 128 : 64));
     dim3 grid(n, groups);
     if (dt == WF_BF16) group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const __nv_bfloat16*)w, gw, eps, res, y, ldy, (__nv_bfloat16*)y_t, ldt, rows);
     else group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const float*)w, gw, eps, res, y, ldy, (float*)y_t, ldt, rows);
@@ -85,9 +85,11 @@ int launch_causal_taps(int dt, const Batch& b, const float* in, int ld_in, const
 
 // thread per (sequence, channel): state[k] <- input at portion index len - (taps - 1) + k, taken from the old state when that is negative.
 // Ascending k is safe in place: entry k reads old entry len + k > k.
-__global__ void taps_state_kernel(Batch b, const float* __restrict__ in, int ld_in, int taps, int C, float* __restrict__ state, size_t slot_stride) {
+__global__ void taps_state_kernel(Batch b, const float* __restrict__ in, int ld_in, int taps, int C, float* __restrict__ state, size_t slot_stride,
+                                  int skip_single) {
     const int sq = blockIdx.x;
     const int len = b.seq_len[sq], start = b.seq_start[sq];
+    if (skip_single && len == 1) return;                 // rolled by the fused norm + taps kernel
     float* st = state + (size_t)b.seq_slot[sq] * slot_stride;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
         for (int k = 0; k < taps - 1; ++k) {
@@ -97,17 +99,93 @@ __global__ void taps_state_kernel(Batch b, const float* __restrict__ in, int ld_
     }
 }
 
-int launch_taps_state(const Batch& b, const float* in, int ld_in, int taps, int C, float* state, size_t slot_stride, cudaStream_t s) {
+int launch_taps_state(const Batch& b, const float* in, int ld_in, int taps, int C, float* state, size_t slot_stride, cudaStream_t s, int skip_single) {
     if (b.nseq <= 0 || taps <= 1) return WF_OK;
     dim3 grid(b.nseq, (C + 255) / 256 > 8 ? 8 : (C + 255) / 256);
-    taps_state_kernel<<<grid, 256, 0, s>>>(b, in, ld_in, taps, C, state, slot_stride);
+    taps_state_kernel<<<grid, 256, 0, s>>>(b, in, ld_in, taps, C, state, slot_stride, skip_single);
     return launch_check(cudaGetLastError(), "taps_state");
+}
+
+// ---- grouped RMS norm fused with the input convolution that follows it ---------------------------------------------------------
+// One block per token: it normalises the token's own row and the taps - 1 rows before it (those inside this step's portion; earlier ones
+// come normalised from the carried state), applies the taps, and writes the operand of the sublayer's matrix products.  Rows that the
+// next step will need are also written as float (hn) for the state roll; a sequence that brings a single token rolls its state here.
+constexpr int NTAPS_MAX = 8;
+
+template <typename T>
+__global__ void norm_taps_kernel(Batch b, const float* __restrict__ x, int ldx, const T* __restrict__ nw, int groups, float eps, const T* __restrict__ cw,
+                                 int taps, int W, float* __restrict__ state, size_t slot_stride, T* __restrict__ out_t, int ld_t, float* __restrict__ hn) {
+    __shared__ float red[NTAPS_MAX][33];
+    __shared__ float inv[NTAPS_MAX * 32];            // [tap][group]
+    const int i = blockIdx.x;
+    const int sq = b.tok_seq[i];
+    const int li = i - b.seq_start[sq], len = b.seq_len[sq];
+    const int gw = W / groups;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw_ = blockDim.x >> 5;
+    float* st = state + (size_t)b.seq_slot[sq] * slot_stride;
+    for (int g = 0; g < groups; ++g) {
+        float ss[NTAPS_MAX];
+#pragma unroll
+        for (int j = 0; j < NTAPS_MAX; ++j) ss[j] = 0.f;
+        for (int c = threadIdx.x; c < gw; c += blockDim.x) {
+#pragma unroll
+            for (int j = 0; j < NTAPS_MAX; ++j) {
+                const int src = li - (taps - 1) + j;
+                if (j < taps && src >= 0) { const float v = x[(size_t)(i - li + src) * ldx + g * gw + c]; ss[j] += v * v; }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NTAPS_MAX; ++j) {
+            if (j < taps) { const float v = warp_sum(ss[j]); if (lane == 0) red[j][warp] = v; }
+        }
+        __syncthreads();
+        if (threadIdx.x < taps) {
+            float t = 0.f;
+            for (int w = 0; w < nw_; ++w) t += red[threadIdx.x][w];
+            inv[threadIdx.x * 32 + g] = 1.f / sqrtf(t / (float)gw + eps);
+        }
+        __syncthreads();
+    }
+    const bool keep = li >= len - (taps - 1);        // one of the last taps - 1 rows of the portion: the next step's state
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const int g = c / gw;
+        const float wn = to_f(nw[c]);
+        float acc = 0.f, cur = 0.f, old[NTAPS_MAX];
+#pragma unroll
+        for (int j = 0; j < NTAPS_MAX; ++j) {
+            if (j < taps) {
+                const int src = li - (taps - 1) + j;
+                float v;
+                if (src >= 0) v = x[(size_t)(i - li + src) * ldx + c] * inv[j * 32 + g] * wn;
+                else v = st[(size_t)(src + taps - 1) * W + c];
+                old[j] = v;
+                acc = fmaf(to_f(cw[(size_t)c * taps + j]), v, acc);
+                if (j == taps - 1) cur = v;
+            }
+        }
+        out_t[(size_t)i * ld_t + c] = from_f<T>(cur + acc);
+        if (keep && hn) hn[(size_t)i * W + c] = cur;
+        if (len == 1) {                               // old[j] is the input at distance taps - 1 - j: the new tail is old[1 .. taps - 1]
+#pragma unroll
+            for (int j = 1; j < NTAPS_MAX; ++j) if (j < taps) st[(size_t)(j - 1) * W + c] = old[j];
+        }
+    }
+}
+
+int launch_norm_taps(int dt, const Batch& b, const float* x, int ldx, const void* nw, int groups, float eps, const void* cw, int taps, int W, float* state,
+                     size_t slot_stride, void* out_t, int ld_t, float* hn, cudaStream_t s) {
+    if (b.n <= 0) return WF_OK;
+    if (!norm_taps_usable(groups, taps, W)) { set_error("norm_taps: %d groups / %d taps are beyond the fused kernel", groups, taps); return WF_ERR_UNSUPPORTED; }
+    const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+    if (dt == WF_BF16) norm_taps_kernel<<<b.n, threads, 0, s>>>(b, x, ldx, (const __nv_bfloat16*)nw, groups, eps, (const __nv_bfloat16*)cw, taps, W, state, slot_stride, (__nv_bfloat16*)out_t, ld_t, hn);
+    else norm_taps_kernel<<<b.n, threads, 0, s>>>(b, x, ldx, (const float*)nw, groups, eps, (const float*)cw, taps, W, state, slot_stride, (float*)out_t, ld_t, hn);
+    return launch_check(cudaGetLastError(), "norm_taps");
 }
 
 template <typename T>
 __global__ void gate_mul_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ g, int ldg, int act, int C, T* __restrict__ y, int ldy) {
     const int i = blockIdx.x;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
         const float z = g[(size_t)i * ldg + c];
         y[(size_t)i * ldy + c] = from_f<T>(x[(size_t)i * ldx + c] * (act == 2 ? 1.f : (act ? silu_f(z) : sigmoid_f(z))));
     }
@@ -115,8 +193,9 @@ __global__ void gate_mul_kernel(const float* __restrict__ x, int ldx, const floa
 
 int launch_gate_mul(int dt, const float* x, int ldx, const float* g, int ldg, int act, int n, int C, void* y, int ldy, cudaStream_t s) {
     if (n <= 0) return WF_OK;
-    if (dt == WF_BF16) gate_mul_kernel<<<n, 256, 0, s>>>(x, ldx, g, ldg, act, C, (__nv_bfloat16*)y, ldy);
-    else gate_mul_kernel<<<n, 256, 0, s>>>(x, ldx, g, ldg, act, C, (float*)y, ldy);
+    const dim3 grid(n, n < 64 ? (C + 255) / 256 : 1);
+    if (dt == WF_BF16) gate_mul_kernel<<<grid, 256, 0, s>>>(x, ldx, g, ldg, act, C, (__nv_bfloat16*)y, ldy);
+    else gate_mul_kernel<<<grid, 256, 0, s>>>(x, ldx, g, ldg, act, C, (float*)y, ldy);
     return launch_check(cudaGetLastError(), "gate_mul");
 }
 
