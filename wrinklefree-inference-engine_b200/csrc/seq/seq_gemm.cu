@@ -1,5 +1,5 @@
 // Dense, batched and grouped matrix products of the sequence models: C[m, n] = sum_k A[m, k] * B[n, k] with float accumulation.
-//   * gemm_simt_kernel — any storage type, plain FMA (the all-32-bit mode, and the checker of the tensor-core form);
+//   * gemm_simt_kernel — any storage type, plain FMA (the all-32-bit mode; the tests compare the tensor-core forms with it);
 //   * gemm_mma_kernel  — bf16 operands on mma.sync.m16n8k16 with a cp.async double buffer (the serving mode).
 // Both take the same GemmArgs: grid.z batches with strides (per-head up-projections), or the grouped form in which every 64-row tile
 // names its own weight matrix (routed experts) and A rows may be gathered through an index list.
