@@ -474,3 +474,25 @@ def test_grouped_matrix_product_on_the_tensor_cores():
             else:
                 want = A[rows].double() @ B[e].double().T
                 assert (got[rows].double() - want).abs().max() < 2e-3 * (1 + want.abs().max()), (algo, t)
+
+
+@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(20, 128, 16), (5, 512, 32), (33, 256, 8)])
+def test_latent_attention_on_tensor_cores_with_key_splits(heads, kv_rank, rot_dim):
+    """Sizes that take the tensor-core attention kernel (latent a multiple of 32): padded head tiles, several head tiles, and a window
+    long enough that single decoded tokens have their keys split over several CTAs and merged."""
+    cfg = config([lat(heads=heads, dim=16, rot_dim=rot_dim, vdim=16, kv_rank=kv_rank, window=600, scale=0.5)], width=64, vocab=40, groups=1, taps=2)
+    w = make_weights(cfg, 61)
+    m = build(cfg, w, "bfloat16", max_tokens=768, page_size=16, max_step_tokens=256)
+    n = 700
+    x = _rows(n, 64, 62)
+    P = {k: torch.from_numpy(v).double() for k, v in O.sub(w, "l0.mix.").items()}
+    want = O.latent_attention(torch.from_numpy(x).double(), P, cfg["layers"][0]["mixer"], 1e-6).numpy()
+    s = m.admit()
+    cuts = [256, 256, 170, 3, 2] + [1] * 13
+    got, a = [], 0
+    for c in cuts:
+        got.append(m.engine.run_part(0, 2, [s], [c], x[a:a + c]))
+        a += c
+    err = rel_err(np.concatenate(got), want)
+    assert err.max() < TOL["bfloat16"], (int(err.argmax()), err.max())
+    m.close()
