@@ -73,7 +73,7 @@ struct wf_seq_engine {
     int32_t *ids = nullptr, *counts = nullptr, *plan_scratch = nullptr, *sorted_rows = nullptr, *pair_row = nullptr, *tile_group = nullptr;
     int P = 0;                        // padded expert-row bound
     int fuse_input = 1;               // norm + input convolution (+ state roll of single-token sequences) in one kernel (WF_SEQ_FUSE_INPUT=0: three kernels)
-    int attn_mma = 1;                 // latent attention on tensor cores where the sizes allow it (WF_SEQ_ATTN_MMA=0: the plain kernel)
+    int attn_mma = 2;                 // latent attention on tensor cores where the sizes allow it: 2 keys-as-rows form first, 1 heads-as-rows form only, 0 plain kernel (WF_SEQ_ATTN_MMA)
     float* attn_ws = nullptr;         // partial results of key-split attention
     int attn_ws_rows = 0;             // token-splits it holds
     int pair_path_max = 64;           // up to this many (token, expert) pairs the experts run as per-pair weight streams (WF_SEQ_PAIR_MAX)
@@ -242,20 +242,24 @@ int run_latent(wf_seq_engine* e, LayerState& L, const Batch& b) {
         if ((rc = launch_gemm(e->dt, g, s))) return rc;
         mark(e, "latent.absorb_gemm");
     }
-    if (e->dt == WF_BF16 && e->attn_mma && latent_attn_mma_usable(D) && L.cache_off % 8 == 0 && e->page_stride % 8 == 0) {
-        // few query tokens and a long window: split the keys so that the machine is busy
+    const bool rows_ok = L.cache_off % 8 == 0 && e->page_stride % 8 == 0;       // cached rows start 16-byte aligned
+    const bool use_kt = e->dt == WF_BF16 && e->attn_mma >= 2 && rows_ok && latent_attn_kt_usable(D);
+    const bool use_ht = e->dt == WF_BF16 && e->attn_mma >= 1 && rows_ok && !use_kt && latent_attn_mma_usable(D);
+    if (use_kt || use_ht) {
+        // few query tokens and a long window: split the keys so that one resident wave of CTAs covers the machine
         // (a CTA holds Q, two key tiles and P in shared memory: that decides how many are resident at once)
         int splits = 1;
         const int span = c.window < e->cfg.max_pages * e->cfg.page_size ? c.window : e->cfg.max_pages * e->cfg.page_size;
-        const int resident = sm_count() * latent_attn_mma_ctas_per_sm(D);
+        const int resident = sm_count() * (use_kt ? latent_attn_kt_ctas_per_sm(D) : latent_attn_mma_ctas_per_sm(D));
         if (2 * n <= resident) {
-            splits = resident / n;                               // one full wave, no second partial one
+            splits = resident / n;
             if (splits > span / 128) splits = span / 128;
             if (splits > e->attn_ws_rows / n) splits = e->attn_ws_rows / n;
             if (splits > 16) splits = 16;
             if (splits < 1) splits = 1;
         }
-        if ((rc = launch_latent_attn_mma(b, D, e->qa, e->qr, pc, e->olat, e->attn_ws, splits, s))) return rc;
+        if (use_kt) { if ((rc = launch_latent_attn_kt(b, D, e->qa, e->qr, pc, e->olat, e->attn_ws, splits, s))) return rc; }
+        else if ((rc = launch_latent_attn_mma(b, D, e->qa, e->qr, pc, e->olat, e->attn_ws, splits, s))) return rc;
     } else if ((rc = launch_latent_attn(e->dt, b, D, e->qa, e->qr, pc, e->olat, s))) return rc;
     mark(e, "latent.attention");
     {   // ov[i, h, :] = W_uv[h] olat[i, h, :]

@@ -75,7 +75,12 @@ int launch_latent_attn(int dt, const Batch& b, const LatentDims& L, const float*
 // workspace for n * splits partial results (latent_attn_mma_workspace(n * splits, H, R) bytes).  The cache rows must start 16-byte aligned.
 bool latent_attn_mma_usable(const LatentDims& L);
 size_t latent_attn_mma_workspace(int token_splits, int H, int R);
-int latent_attn_mma_ctas_per_sm(const LatentDims& L);   // resident CTAs per SM (shared-memory bound)
+int latent_attn_mma_ctas_per_sm(const LatentDims& L);
+// the same with the keys as the M rows of the tiles and the heads as 8-wide N tiles (up to 32 heads, latent a multiple of 16 up to 512)
+bool latent_attn_kt_usable(const LatentDims& L);
+int latent_attn_kt_ctas_per_sm(const LatentDims& L);
+int launch_latent_attn_kt(const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, float* workspace,
+                          int splits, cudaStream_t s);   // resident CTAs per SM (shared-memory bound)
 int launch_latent_attn_mma(const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, float* workspace,
                            int splits, cudaStream_t s);
 // y T [n, C] = x float [n, C] (ldx) * act(g float [n, C] (ldg)); act 0 = sigmoid, 1 = silu, 2 = none (a plain conversion of x)

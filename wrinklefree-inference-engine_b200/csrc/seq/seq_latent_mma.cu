@@ -24,6 +24,9 @@ __device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
 __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
 }
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t (&r)[2], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
+}
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -230,6 +233,199 @@ __global__ void latent_attn_merge_kernel(int H, int R, int splits, const float* 
     }
 }
 
+
+// ---- second form: keys as the M rows ---------------------------------------------------------------------------------------------
+// S^T[key, head] = K[key, :] . Q[head, :]^T and O^T[dim, head] = C^T[dim, key] . P[key, head]: a cached row's fragment is loaded once
+// for ALL heads (heads are 8-wide N tiles: H = 20 pads to 24, not 32), and the queries are the small operand.  8 warps per CTA:
+//   scores: warp (m-tile of 16 keys, quarter of the feature dimension) -> partial S^T in shared memory (fp32);
+//   softmax: warp w owns heads w, w + 8, ..., lanes = the tile's 32 keys; probabilities to shared memory as bf16, rescale factors beside;
+//   values: warp w owns latent m-tiles w, w + 8, ... for all heads.
+template <int NH, int MTW>
+__global__ void __launch_bounds__(256) latent_attn_kt_kernel(Batch b, LatentDims L, const float* __restrict__ qa, const float* __restrict__ qr, PagedCache pc,
+                                                             __nv_bfloat16* __restrict__ out, MmaParams mp) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    constexpr int HP = NH * 8, PS = HP + 1, PT = HP + 8;
+    const int stride = mp.stride, width = L.R + L.r;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);                 // [HP][stride]
+    __nv_bfloat16* Ks = Qs + (size_t)HP * stride;                                // [2][KT][stride]
+    __nv_bfloat16* Pt = Ks + (size_t)2 * KT * stride;                            // [KT][PT] probabilities, bf16
+    float* part = reinterpret_cast<float*>(Pt + KT * PT);                        // [4][KT][PS] partial scores of the four feature quarters
+    float* corr_s = part + 4 * KT * PS;                                          // [HP] rescale factor of the running sums for this tile
+    float* ml_s = corr_s + HP;                                                   // [2][HP] final max and sum
+    const int i = blockIdx.x, split = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sq = b.tok_seq[i], pos = b.tok_pos[i];
+    const int lo_all = pos - L.window + 1 > 0 ? pos - L.window + 1 : 0;
+    const int cnt = pos + 1 - lo_all;
+    int chunk = (cnt + mp.splits - 1) / mp.splits;
+    chunk = (chunk + KT - 1) / KT * KT;
+    const int lo = lo_all + split * chunk;
+    const int hi = lo + chunk < pos + 1 ? lo + chunk : pos + 1;
+    const int32_t* bt = pc.block_table + (size_t)b.seq_slot[sq] * pc.max_blocks;
+
+    for (int h = warp; h < HP; h += 8) {
+        __nv_bfloat16* qd = Qs + (size_t)h * stride;
+        const float* a_src = qa + ((size_t)i * L.H + h) * L.R;
+        const float* r_src = qr + ((size_t)i * L.H + h) * L.r;
+        for (int c = lane; c < mp.dkp; c += 32) {
+            float v = 0.f;
+            if (h < L.H) {
+                if (c < L.R) v = a_src[c];
+                else if (c < width) v = r_src[c - L.R];
+            }
+            qd[c] = __float2bfloat16_rn(v);
+        }
+    }
+    const int chunks_per_row = mp.dkp / 8;
+    const int st_row = tid >> 3, st_sub = tid & 7;                                // 8 threads per key row
+    auto stage = [&](int buf, int j0) {
+        __nv_bfloat16* d = Ks + ((size_t)buf * KT + st_row) * stride;
+        const int j = j0 + st_row;
+        if (j < hi) {
+            const int page = bt[j / pc.page_size];
+            const __nv_bfloat16* src = (const __nv_bfloat16*)pc.pool + (size_t)page * pc.page_stride + pc.layer_off + (size_t)(j % pc.page_size) * width;
+            for (int c = st_sub; c < chunks_per_row; c += 8) {
+                if (c * 8 + 8 <= width) cp_async16(d + c * 8, src + c * 8);
+                else *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        } else {
+            for (int c = st_sub; c < chunks_per_row; c += 8) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        cp_async_commit();
+    };
+    float o[MTW][NH][4];
+#pragma unroll
+    for (int a = 0; a < MTW; ++a)
+#pragma unroll
+        for (int n = 0; n < NH; ++n) { o[a][n][0] = o[a][n][1] = o[a][n][2] = o[a][n][3] = 0.f; }
+    // softmax state of the heads this warp owns (uniform over its lanes)
+    float m_run[(NH + 0)], l_run[(NH + 0)];
+#pragma unroll
+    for (int k = 0; k < NH; ++k) { m_run[k] = -INFINITY; l_run[k] = 0.f; }
+    const int mt = warp & 1, ks = warp >> 1;                                     // score phase: key m-tile, feature quarter
+    const int ksteps = mp.dkp / 16;
+    const int k_lo = ks * ((ksteps + 3) / 4), k_hi = k_lo + (ksteps + 3) / 4 < ksteps ? k_lo + (ksteps + 3) / 4 : ksteps;
+    const int r0 = lane >> 2, cq = (lane & 3) * 2;
+    const int m_tiles = L.R / 16;
+    const int ntiles = hi > lo ? (hi - lo + KT - 1) / KT : 0;
+    if (ntiles > 0) stage(0, lo);
+    for (int t = 0; t < ntiles; ++t) {
+        const int buf = t & 1;
+        cp_async_wait<0>();
+        __syncthreads();
+        if (t + 1 < ntiles) stage(buf ^ 1, lo + (t + 1) * KT);
+        const __nv_bfloat16* Kt = Ks + (size_t)buf * KT * stride;
+        {   // ---- partial scores: 16 keys x all heads over this warp's quarter of the features
+            float s[NH][4];
+#pragma unroll
+            for (int n = 0; n < NH; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+            const __nv_bfloat16* krow = Kt + (size_t)(mt * 16 + (lane & 15)) * stride + (lane >> 4) * 8;
+            const __nv_bfloat16* qrow = Qs + (size_t)(lane & 7) * stride + ((lane >> 3) & 1) * 8;
+            for (int kk = k_lo; kk < k_hi; ++kk) {
+                uint32_t a[4];
+                ldsm_x4(a, krow + kk * 16);
+#pragma unroll
+                for (int n = 0; n < NH; ++n) {
+                    uint32_t bb[2];
+                    ldsm_x2(bb, qrow + (size_t)n * 8 * stride + kk * 16);
+                    mma16816(s[n], a, bb[0], bb[1]);
+                }
+            }
+            float* pd = part + (size_t)ks * KT * PS;
+#pragma unroll
+            for (int n = 0; n < NH; ++n) {
+                pd[(mt * 16 + r0) * PS + n * 8 + cq] = s[n][0];
+                pd[(mt * 16 + r0) * PS + n * 8 + cq + 1] = s[n][1];
+                pd[(mt * 16 + r0 + 8) * PS + n * 8 + cq] = s[n][2];
+                pd[(mt * 16 + r0 + 8) * PS + n * 8 + cq + 1] = s[n][3];
+            }
+        }
+        __syncthreads();
+        {   // ---- softmax of this warp's heads over the tile's 32 keys (lane = key)
+            const int j = lo + t * KT + lane;
+#pragma unroll
+            for (int k = 0; k < NH; ++k) {
+                const int h = warp + 8 * k;
+                float sc = part[lane * PS + h] + part[(KT + lane) * PS + h] + part[(2 * KT + lane) * PS + h] + part[(3 * KT + lane) * PS + h];
+                sc = j < hi ? sc * L.scale : -INFINITY;
+                const float mn = fmaxf(m_run[k], warp_max(sc));                  // finite: the tile's first key exists
+                const float cr = expf(m_run[k] - mn);
+                const float p = expf(sc - mn);
+                l_run[k] = l_run[k] * cr + warp_sum(p);
+                m_run[k] = mn;
+                Pt[lane * PT + h] = __float2bfloat16_rn(p);
+                if (lane == 0) corr_s[h] = cr;
+            }
+        }
+        __syncthreads();
+        {   // ---- O^T[dims of this warp's m-tiles, heads] = O^T * corr + C^T . P
+            float cr[NH][2];
+#pragma unroll
+            for (int n = 0; n < NH; ++n) { cr[n][0] = corr_s[n * 8 + cq]; cr[n][1] = corr_s[n * 8 + cq + 1]; }
+#pragma unroll
+            for (int a = 0; a < MTW; ++a)
+#pragma unroll
+                for (int n = 0; n < NH; ++n) { o[a][n][0] *= cr[n][0]; o[a][n][1] *= cr[n][1]; o[a][n][2] *= cr[n][0]; o[a][n][3] *= cr[n][1]; }
+#pragma unroll
+            for (int k0 = 0; k0 < KT; k0 += 16) {
+                uint32_t pb[NH][2];
+#pragma unroll
+                for (int n = 0; n < NH; ++n) ldsm_x2_trans(pb[n], Pt + (size_t)(k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * PT + n * 8);
+#pragma unroll
+                for (int a = 0; a < MTW; ++a) {
+                    const int mtile = warp + 8 * a;
+                    if (mtile < m_tiles) {
+                        uint32_t af[4];
+                        // A[m = dim][k = key] from rows stored [key][dim]: transposed 8x8 blocks (dims 0-7 | 8-15) x (keys 0-7 | 8-15)
+                        ldsm_x4_trans(af, Kt + (size_t)(k0 + (lane & 7) + (lane >> 4) * 8) * stride + mtile * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+                        for (int n = 0; n < NH; ++n) mma16816(o[a][n], af, pb[n][0], pb[n][1]);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < NH; ++k) { ml_s[warp + 8 * k] = m_run[k]; ml_s[HP + warp + 8 * k] = l_run[k]; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int a = 0; a < MTW; ++a) {
+        const int mtile = warp + 8 * a;
+        if (mtile >= m_tiles) continue;
+#pragma unroll
+        for (int n = 0; n < NH; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = n * 8 + cq + (e & 1), dim = mtile * 16 + r0 + (e >> 1) * 8;
+                if (h >= L.H) continue;
+                if (mp.splits == 1) out[((size_t)i * L.H + h) * L.R + dim] = __float2bfloat16_rn(o[a][n][e] / ml_s[HP + h]);
+                else mp.part[(((size_t)i * mp.splits + split) * L.H + h) * (L.R + 2) + dim] = o[a][n][e];
+            }
+    }
+    if (mp.splits > 1)
+        for (int h = tid; h < L.H; h += blockDim.x) {
+            float* dst = mp.part + (((size_t)i * mp.splits + split) * L.H + h) * (L.R + 2);
+            dst[L.R] = ml_s[h]; dst[L.R + 1] = ml_s[HP + h];
+        }
+}
+
+size_t kt_smem(int NH, const LatentDims& L) {
+    const int HP = NH * 8, dkp = (L.R + L.r + 15) / 16 * 16, stride = dkp + 8;
+    return ((size_t)HP * stride + 2 * KT * stride + (size_t)KT * (HP + 8)) * 2 + ((size_t)4 * KT * (HP + 1) + 3 * HP) * 4;
+}
+
+template <int NH, int MTW>
+int launch_kt(const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, const MmaParams& mp, cudaStream_t s) {
+    static DevOnce once;
+    if (once.need()) cudaFuncSetAttribute(latent_attn_kt_kernel<NH, MTW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    dim3 grid(b.n, mp.splits);
+    latent_attn_kt_kernel<NH, MTW><<<grid, 256, kt_smem(NH, L), s>>>(b, L, qa, qr, pc, (__nv_bfloat16*)out, mp);
+    return launch_check(cudaGetLastError(), "latent_attn_kt");
+}
+
 template <int NT>
 int launch_nt(const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, const MmaParams& mp, size_t smem,
               cudaStream_t s) {
@@ -244,6 +440,44 @@ int launch_nt(const Batch& b, const LatentDims& L, const float* qa, const float*
 }  // namespace
 
 size_t latent_attn_mma_workspace(int token_splits, int H, int R) { return (size_t)token_splits * H * (R + 2) * sizeof(float); }
+
+// the keys-as-rows form takes up to 32 heads and latents that are multiples of 16 up to 512
+bool latent_attn_kt_usable(const LatentDims& L) {
+    if (L.R % 16 || (L.R + L.r) % 8 || L.H > 32 || L.R > 512) return false;
+    return kt_smem((L.H + 7) / 8, L) <= 200 * 1024;
+}
+int latent_attn_kt_ctas_per_sm(const LatentDims& L) {
+    int k = (int)((227 * 1024) / (kt_smem((L.H + 7) / 8, L) + 1024));
+    if (k > 8) k = 8;
+    return k < 1 ? 1 : k;
+}
+
+int launch_latent_attn_kt(const Batch& b, const LatentDims& L, const float* qa, const float* qr, const PagedCache& pc, void* out, float* workspace,
+                          int splits, cudaStream_t s) {
+    if (b.n <= 0) return WF_OK;
+    MmaParams mp;
+    mp.splits = splits < 1 ? 1 : (splits > 16 ? 16 : splits);
+    mp.part = workspace;
+    mp.dkp = (L.R + L.r + 15) / 16 * 16;
+    mp.stride = mp.dkp + 8;
+    if (mp.splits > 1 && !workspace) mp.splits = 1;
+    const int NH = (L.H + 7) / 8, mtw = (L.R / 16 + 7) / 8;
+    int rc = WF_ERR_UNSUPPORTED;
+#define KT_CASE(nh, mw) if (NH == nh && mtw == mw) rc = launch_kt<nh, mw>(b, L, qa, qr, pc, out, mp, s);
+    KT_CASE(1, 1) KT_CASE(1, 2) KT_CASE(1, 3) KT_CASE(1, 4)
+    KT_CASE(2, 1) KT_CASE(2, 2) KT_CASE(2, 3) KT_CASE(2, 4)
+    KT_CASE(3, 1) KT_CASE(3, 2) KT_CASE(3, 3) KT_CASE(3, 4)
+    KT_CASE(4, 1) KT_CASE(4, 2) KT_CASE(4, 3) KT_CASE(4, 4)
+#undef KT_CASE
+    if (rc == WF_ERR_UNSUPPORTED) set_error("latent_attn_kt: unsupported sizes (heads %d, latent %d)", L.H, L.R);
+    if (rc) return rc;
+    if (mp.splits > 1) {
+        dim3 grid(b.n, L.H);
+        latent_attn_merge_kernel<<<grid, 128, 0, s>>>(L.H, L.R, mp.splits, workspace, (__nv_bfloat16*)out);
+        return launch_check(cudaGetLastError(), "latent_attn_merge");
+    }
+    return WF_OK;
+}
 
 int latent_attn_mma_ctas_per_sm(const LatentDims& L) {
     const int HT = (L.H + 15) / 16, dkp = (L.R + L.r + 15) / 16 * 16, stride = dkp + 8;
