@@ -240,11 +240,26 @@ __global__ void latent_attn_merge_kernel(int H, int R, int splits, const float* 
 //   scores: warp (m-tile of 16 keys, quarter of the feature dimension) -> partial S^T in shared memory (fp32);
 //   softmax: warp w owns heads w, w + 8, ..., lanes = the tile's 32 keys; probabilities to shared memory as bf16, rescale factors beside;
 //   values: warp w owns latent m-tiles w, w + 8, ... for all heads.
+// 32-bit shared-memory addresses for the fragment loads (no generic-pointer arithmetic inside the tile loop)
+__device__ __forceinline__ void ldsm_x4_a(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_a(uint32_t (&r)[2], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans_a(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_trans_a(uint32_t (&r)[2], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__host__ __device__ constexpr int kt_pt_stride(int NH) { return (NH & 1) ? NH * 8 + 16 : NH * 8 + 8; }   // 16-byte units per row odd: conflict-free ldmatrix
+
 template <int NH, int MTW>
 __global__ void __launch_bounds__(256) latent_attn_kt_kernel(Batch b, LatentDims L, const float* __restrict__ qa, const float* __restrict__ qr, PagedCache pc,
                                                              __nv_bfloat16* __restrict__ out, MmaParams mp) {
     extern __shared__ __align__(16) unsigned char smraw[];
-    constexpr int HP = NH * 8, PS = HP + 1, PT = HP + 8;
+    constexpr int HP = NH * 8, PS = HP + 1, PT = kt_pt_stride(NH);
     const int stride = mp.stride, width = L.R + L.r;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);                 // [HP][stride]
     __nv_bfloat16* Ks = Qs + (size_t)HP * stride;                                // [2][KT][stride]
@@ -276,20 +291,26 @@ __global__ void __launch_bounds__(256) latent_attn_kt_kernel(Batch b, LatentDims
             qd[c] = __float2bfloat16_rn(v);
         }
     }
-    const int chunks_per_row = mp.dkp / 8;
-    const int st_row = tid >> 3, st_sub = tid & 7;                                // 8 threads per key row
+    // staging: 8 threads per key row, 16-byte chunks.  The padding columns (width .. dkp) of both buffers are zeroed once; rows past
+    // `hi` (last tile only) are zeroed when they occur.
+    const int full_chunks = width / 8, chunks_per_row = mp.dkp / 8;
+    const int st_row = tid >> 3, st_sub = tid & 7;
+    for (int bf = 0; bf < 2; ++bf)
+        for (int c = full_chunks + st_sub; c < chunks_per_row; c += 8)
+            *reinterpret_cast<uint4*>(Ks + ((size_t)bf * KT + st_row) * stride + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t ks_base = smem_u32(Ks);
+    const uint32_t st_dst0 = ks_base + (uint32_t)(st_row * stride + st_sub * 8) * 2u;
     auto stage = [&](int buf, int j0) {
-        __nv_bfloat16* d = Ks + ((size_t)buf * KT + st_row) * stride;
+        const uint32_t d = st_dst0 + (uint32_t)buf * (uint32_t)(KT * stride * 2);
         const int j = j0 + st_row;
         if (j < hi) {
             const int page = bt[j / pc.page_size];
-            const __nv_bfloat16* src = (const __nv_bfloat16*)pc.pool + (size_t)page * pc.page_stride + pc.layer_off + (size_t)(j % pc.page_size) * width;
-            for (int c = st_sub; c < chunks_per_row; c += 8) {
-                if (c * 8 + 8 <= width) cp_async16(d + c * 8, src + c * 8);
-                else *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0u, 0u, 0u, 0u);
-            }
+            const __nv_bfloat16* src = (const __nv_bfloat16*)pc.pool + (size_t)page * pc.page_stride + pc.layer_off + (size_t)(j % pc.page_size) * width + st_sub * 8;
+            for (int c = st_sub; c < full_chunks; c += 8, src += 64)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + (uint32_t)(c - st_sub) * 16u), "l"(src) : "memory");
         } else {
-            for (int c = st_sub; c < chunks_per_row; c += 8) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            for (int c = st_sub; c < full_chunks; c += 8)
+                asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(d + (uint32_t)(c - st_sub) * 16u), "r"(0u) : "memory");
         }
         cp_async_commit();
     };
@@ -298,15 +319,22 @@ __global__ void __launch_bounds__(256) latent_attn_kt_kernel(Batch b, LatentDims
     for (int a = 0; a < MTW; ++a)
 #pragma unroll
         for (int n = 0; n < NH; ++n) { o[a][n][0] = o[a][n][1] = o[a][n][2] = o[a][n][3] = 0.f; }
-    // softmax state of the heads this warp owns (uniform over its lanes)
-    float m_run[(NH + 0)], l_run[(NH + 0)];
+    float m_run[NH], l_run[NH];                                                  // softmax state of the heads this warp owns (uniform over its lanes)
 #pragma unroll
     for (int k = 0; k < NH; ++k) { m_run[k] = -INFINITY; l_run[k] = 0.f; }
     const int mt = warp & 1, ks = warp >> 1;                                     // score phase: key m-tile, feature quarter
     const int ksteps = mp.dkp / 16;
-    const int k_lo = ks * ((ksteps + 3) / 4), k_hi = k_lo + (ksteps + 3) / 4 < ksteps ? k_lo + (ksteps + 3) / 4 : ksteps;
+    const int k_per = (ksteps + 3) / 4;
+    const int k_lo = ks * k_per, k_hi = k_lo + k_per < ksteps ? k_lo + k_per : ksteps;
     const int r0 = lane >> 2, cq = (lane & 3) * 2;
     const int m_tiles = L.R / 16;
+    const uint32_t tile_bytes = (uint32_t)(KT * stride * 2);
+    // per-lane fragment addresses (bytes, shared window)
+    const uint32_t k_frag = ks_base + (uint32_t)((mt * 16 + (lane & 15)) * stride + (lane >> 4) * 8 + k_lo * 16) * 2u;
+    const uint32_t q_frag = smem_u32(Qs) + (uint32_t)((lane & 7) * stride + ((lane >> 3) & 1) * 8 + k_lo * 16) * 2u;
+    const uint32_t c_frag = ks_base + (uint32_t)(((lane & 7) + (lane >> 4) * 8) * stride + ((lane >> 3) & 1) * 8) * 2u;
+    const uint32_t p_frag = smem_u32(Pt) + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * PT) * 2u;
+    float* part_w = part + (size_t)ks * KT * PS + (mt * 16 + r0) * PS + cq;
     const int ntiles = hi > lo ? (hi - lo + KT - 1) / KT : 0;
     if (ntiles > 0) stage(0, lo);
     for (int t = 0; t < ntiles; ++t) {
@@ -314,70 +342,92 @@ __global__ void __launch_bounds__(256) latent_attn_kt_kernel(Batch b, LatentDims
         cp_async_wait<0>();
         __syncthreads();
         if (t + 1 < ntiles) stage(buf ^ 1, lo + (t + 1) * KT);
-        const __nv_bfloat16* Kt = Ks + (size_t)buf * KT * stride;
+        const uint32_t kt_off = (uint32_t)buf * tile_bytes;
         {   // ---- partial scores: 16 keys x all heads over this warp's quarter of the features
             float s[NH][4];
 #pragma unroll
             for (int n = 0; n < NH; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
-            const __nv_bfloat16* krow = Kt + (size_t)(mt * 16 + (lane & 15)) * stride + (lane >> 4) * 8;
-            const __nv_bfloat16* qrow = Qs + (size_t)(lane & 7) * stride + ((lane >> 3) & 1) * 8;
-            for (int kk = k_lo; kk < k_hi; ++kk) {
+            uint32_t ka = k_frag + kt_off, qa_ = q_frag;
+            for (int kk = k_lo; kk < k_hi; ++kk, ka += 32u, qa_ += 32u) {
                 uint32_t a[4];
-                ldsm_x4(a, krow + kk * 16);
+                ldsm_x4_a(a, ka);
 #pragma unroll
                 for (int n = 0; n < NH; ++n) {
                     uint32_t bb[2];
-                    ldsm_x2(bb, qrow + (size_t)n * 8 * stride + kk * 16);
+                    ldsm_x2_a(bb, qa_ + (uint32_t)(n * 8 * stride * 2));
                     mma16816(s[n], a, bb[0], bb[1]);
                 }
             }
-            float* pd = part + (size_t)ks * KT * PS;
 #pragma unroll
             for (int n = 0; n < NH; ++n) {
-                pd[(mt * 16 + r0) * PS + n * 8 + cq] = s[n][0];
-                pd[(mt * 16 + r0) * PS + n * 8 + cq + 1] = s[n][1];
-                pd[(mt * 16 + r0 + 8) * PS + n * 8 + cq] = s[n][2];
-                pd[(mt * 16 + r0 + 8) * PS + n * 8 + cq + 1] = s[n][3];
+                part_w[n * 8] = s[n][0];
+                part_w[n * 8 + 1] = s[n][1];
+                part_w[8 * PS + n * 8] = s[n][2];
+                part_w[8 * PS + n * 8 + 1] = s[n][3];
             }
         }
         __syncthreads();
+        bool rescale = false;
         {   // ---- softmax of this warp's heads over the tile's 32 keys (lane = key)
             const int j = lo + t * KT + lane;
+            const bool valid = j < hi;
+            float sc[NH], mx[NH];
 #pragma unroll
             for (int k = 0; k < NH; ++k) {
-                const int h = warp + 8 * k;
-                float sc = part[lane * PS + h] + part[(KT + lane) * PS + h] + part[(2 * KT + lane) * PS + h] + part[(3 * KT + lane) * PS + h];
-                sc = j < hi ? sc * L.scale : -INFINITY;
-                const float mn = fmaxf(m_run[k], warp_max(sc));                  // finite: the tile's first key exists
-                const float cr = expf(m_run[k] - mn);
-                const float p = expf(sc - mn);
-                l_run[k] = l_run[k] * cr + warp_sum(p);
+                const float* pp = part + lane * PS + warp + 8 * k;
+                const float v = pp[0] + pp[KT * PS] + pp[2 * KT * PS] + pp[3 * KT * PS];
+                sc[k] = valid ? v * L.scale : -INFINITY;
+                mx[k] = sc[k];
+            }
+#pragma unroll
+            for (int o_ = 16; o_ > 0; o_ >>= 1)
+#pragma unroll
+                for (int k = 0; k < NH; ++k) mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o_));
+            float p[NH], ps[NH], cr[NH];
+#pragma unroll
+            for (int k = 0; k < NH; ++k) {
+                const float mn = fmaxf(m_run[k], mx[k]);                         // finite: the tile's first key exists
+                cr[k] = expf(m_run[k] - mn);
+                p[k] = expf(sc[k] - mn);
+                ps[k] = p[k];
                 m_run[k] = mn;
-                Pt[lane * PT + h] = __float2bfloat16_rn(p);
-                if (lane == 0) corr_s[h] = cr;
+                Pt[lane * PT + warp + 8 * k] = __float2bfloat16_rn(p[k]);
+            }
+#pragma unroll
+            for (int o_ = 16; o_ > 0; o_ >>= 1)
+#pragma unroll
+                for (int k = 0; k < NH; ++k) ps[k] += __shfl_xor_sync(0xffffffffu, ps[k], o_);
+#pragma unroll
+            for (int k = 0; k < NH; ++k) {
+                l_run[k] = l_run[k] * cr[k] + ps[k];
+                if (lane == 0) corr_s[warp + 8 * k] = cr[k];
             }
         }
         __syncthreads();
         {   // ---- O^T[dims of this warp's m-tiles, heads] = O^T * corr + C^T . P
             float cr[NH][2];
+            bool one = true;
 #pragma unroll
-            for (int n = 0; n < NH; ++n) { cr[n][0] = corr_s[n * 8 + cq]; cr[n][1] = corr_s[n * 8 + cq + 1]; }
+            for (int n = 0; n < NH; ++n) { cr[n][0] = corr_s[n * 8 + cq]; cr[n][1] = corr_s[n * 8 + cq + 1]; one = one && cr[n][0] == 1.f && cr[n][1] == 1.f; }
+            rescale = !__all_sync(0xffffffffu, one);                             // once the running maxima have settled nothing is rescaled
+            if (rescale) {
 #pragma unroll
-            for (int a = 0; a < MTW; ++a)
+                for (int a = 0; a < MTW; ++a)
 #pragma unroll
-                for (int n = 0; n < NH; ++n) { o[a][n][0] *= cr[n][0]; o[a][n][1] *= cr[n][1]; o[a][n][2] *= cr[n][0]; o[a][n][3] *= cr[n][1]; }
+                    for (int n = 0; n < NH; ++n) { o[a][n][0] *= cr[n][0]; o[a][n][1] *= cr[n][1]; o[a][n][2] *= cr[n][0]; o[a][n][3] *= cr[n][1]; }
+            }
 #pragma unroll
             for (int k0 = 0; k0 < KT; k0 += 16) {
                 uint32_t pb[NH][2];
 #pragma unroll
-                for (int n = 0; n < NH; ++n) ldsm_x2_trans(pb[n], Pt + (size_t)(k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * PT + n * 8);
+                for (int n = 0; n < NH; ++n) ldsm_x2_trans_a(pb[n], p_frag + (uint32_t)((k0 * PT + n * 8) * 2));
 #pragma unroll
                 for (int a = 0; a < MTW; ++a) {
                     const int mtile = warp + 8 * a;
                     if (mtile < m_tiles) {
                         uint32_t af[4];
                         // A[m = dim][k = key] from rows stored [key][dim]: transposed 8x8 blocks (dims 0-7 | 8-15) x (keys 0-7 | 8-15)
-                        ldsm_x4_trans(af, Kt + (size_t)(k0 + (lane & 7) + (lane >> 4) * 8) * stride + mtile * 16 + ((lane >> 3) & 1) * 8);
+                        ldsm_x4_trans_a(af, c_frag + kt_off + (uint32_t)((k0 * stride + mtile * 16) * 2));
 #pragma unroll
                         for (int n = 0; n < NH; ++n) mma16816(o[a][n], af, pb[n][0], pb[n][1]);
                     }
@@ -414,7 +464,7 @@ __global__ void __launch_bounds__(256) latent_attn_kt_kernel(Batch b, LatentDims
 
 size_t kt_smem(int NH, const LatentDims& L) {
     const int HP = NH * 8, dkp = (L.R + L.r + 15) / 16 * 16, stride = dkp + 8;
-    return ((size_t)HP * stride + 2 * KT * stride + (size_t)KT * (HP + 8)) * 2 + ((size_t)4 * KT * (HP + 1) + 3 * HP) * 4;
+    return ((size_t)HP * stride + 2 * KT * stride + (size_t)KT * kt_pt_stride(NH)) * 2 + ((size_t)4 * KT * (HP + 1) + 3 * HP) * 4;
 }
 
 template <int NH, int MTW>
