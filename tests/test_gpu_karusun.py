@@ -136,7 +136,11 @@ CFG_ODD = config([with_ff(delta(heads=4, kv_heads=2, dim=12, vdim=8, conv=2), mo
 CFG_WIDE = config([with_ff(lat(heads=2, dim=32, rot_dim=32, vdim=32, kv_rank=64, window=40), moe(experts=8, identity=2, top=3, count=5, keep=3, ff=48)),
                    with_ff(delta(heads=2, kv_heads=2, dim=72, vdim=40, conv=4), moe(experts=8, identity=2, top=3, count=5, keep=3, ff=48))],
                   width=128, vocab=150, groups=4, taps=2)
-CONFIGS = {"mixed": CFG_MIXED, "odd": CFG_ODD, "wide": CFG_WIDE}
+# nothing here is a multiple of 8: rows of every matrix start unaligned, so the vector / TMA forms of the products must step aside
+CFG_THIN = config([with_ff(lat(heads=3, dim=10, rot_dim=6, vdim=14, kv_rank=22, window=7), moe(experts=5, identity=1, top=2, count=3, keep=2, ff=13)),
+                   with_ff(delta(heads=3, kv_heads=3, dim=10, vdim=14, conv=3), moe(experts=2, identity=2, top=2, count=2, keep=2, ff=9))],
+                  width=36, vocab=31, groups=3, taps=3)
+CONFIGS = {"mixed": CFG_MIXED, "odd": CFG_ODD, "wide": CFG_WIDE, "thin": CFG_THIN}
 
 
 def tokens_for(cfg, n, seed):
@@ -245,7 +249,7 @@ def run_alone(m, tokens, cuts):
     return np.concatenate(out)
 
 
-@pytest.mark.parametrize("name", ["mixed", "odd", "wide"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "wide", "thin"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_prompt_decode_and_portions_agree_with_the_oracle(name, dtype):
     cfg = CONFIGS[name]

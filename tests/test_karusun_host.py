@@ -164,3 +164,30 @@ def test_oracle_convolution_and_recurrence_identities():
     assert set(idx.flatten().tolist()) <= {2, 3}
     s = torch.softmax(x @ P["router"].T, -1)
     assert torch.allclose(wt, s.gather(1, idx))
+
+
+def test_sequence_engine_abi_matches_its_header():
+    """libwf_seq.so exports every function include/wf_seq.h declares, each has a ctypes signature, struct sizes follow the header, and
+    the engine refuses to exist without a device instead of falling back to anything."""
+    import ctypes as C
+    import re
+    from pathlib import Path
+
+    from wf_bitnet import _lib
+    header = (Path(__file__).resolve().parent.parent / "include" / "wf_seq.h").read_text()
+    decl = sorted(set(re.findall(r"\b(wf_seq_[a-z0-9_]+)\s*\(", header)))
+    L = _lib.seq_lib()
+    assert len(decl) >= 20
+    for name in decl:
+        assert hasattr(L, name), f"{name} declared in wf_seq.h but not exported"
+        assert name in _lib.SEQ_SYMBOLS, f"{name} has no ctypes signature"
+    for name in _lib.SEQ_SYMBOLS:
+        assert name in decl or name == "wf_last_error"
+    assert C.sizeof(_lib.SeqLayer) == 19 * 4 and C.sizeof(_lib.SeqConfig) == 11 * 4
+    if not torch.cuda.is_available():
+        assert L.wf_seq_available() == 0
+        from sglang.srt.models.karusun import KarusunForCausalLM
+        cfg = {"architecture": "Karusun", "vocab": 8, "width": 8, "norm": {"eps": 1e-6, "groups": 1}, "canon": {"taps": 1},
+               "layers": [{"type": "delta", "mixer": {"heads": 1, "kv_heads": 1, "dim": 8, "vdim": 8, "conv": 1}, "mlp": None}]}
+        with pytest.raises(_lib.WfError):
+            KarusunForCausalLM(cfg)

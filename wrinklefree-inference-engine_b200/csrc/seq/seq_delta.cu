@@ -30,19 +30,21 @@ __global__ void delta_prep_kernel(DeltaDims D, float* __restrict__ qkv, int ld, 
     }
 }
 
-constexpr int DR_COLS = 32, DR_PARTS = 4, DR_TT = 8;
+constexpr int DR_COLS = 32, DR_PARTS = 4, DR_TT = 16;
 
-// block = (sequence, head, 32 value columns); thread = (column, quarter of the key rows), its part of the column in registers
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+
+// block = (sequence, head, 32 value columns); thread = (column, quarter of the key rows), its part of the column in registers.
+// Tokens are taken 16 at a time: the next group's k / q / v / gates are copied into the other half of shared memory (cp.async)
+// while the current group runs, so the per-token chain is only register math, shared-memory broadcasts and two quad reductions.
 template <int DPT>
 __global__ void __launch_bounds__(DR_COLS * DR_PARTS) delta_rule_kernel(Batch b, DeltaDims D, const float* __restrict__ qkv, int ld,
                                                                          const float* __restrict__ beta, const float* __restrict__ decay,
                                                                          float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
     extern __shared__ float sm[];
-    float* ks = sm;                         // [TT][d]
-    float* qs = ks + DR_TT * D.d;           // [TT][d]
-    float* vs = qs + DR_TT * D.d;           // [TT][32]
-    float* bs = vs + DR_TT * DR_COLS;       // [TT]
-    float* gs = bs + DR_TT;                 // [TT]
+    const int tile_floats = 2 * DR_TT * D.d + DR_TT * DR_COLS + 2 * DR_TT;   // k [TT][d], q [TT][d], v [TT][32], beta [TT], decay [TT]
     const int sq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
     const int tid = threadIdx.x, p = tid % DR_PARTS, jl = tid / DR_PARTS, col = col0 + jl;
     const bool col_ok = col < D.dv;
@@ -56,49 +58,69 @@ __global__ void __launch_bounds__(DR_COLS * DR_PARTS) delta_rule_kernel(Batch b,
         s[m] = (col_ok && i < D.d) ? S[(size_t)i * D.dv + col] : 0.f;
     }
     const int q_off = kh * D.d, k_off = (D.Hk + kh) * D.d, v_off = 2 * D.Hk * D.d + h * D.dv;
-    for (int t0 = 0; t0 < len; t0 += DR_TT) {
+    auto stage = [&](int buf, int t0) {
+        float* ks = sm + (size_t)buf * tile_floats;
+        float* qs = ks + DR_TT * D.d;
+        float* vs = qs + DR_TT * D.d;
+        float* bs = vs + DR_TT * DR_COLS;
+        float* gs = bs + DR_TT;
         const int tt = len - t0 < DR_TT ? len - t0 : DR_TT;
-        __syncthreads();
         for (int idx = tid; idx < tt * D.d; idx += blockDim.x) {
-            const int t = idx / D.d, c = idx % D.d;
+            const int t = idx / D.d, c = idx - t * D.d;
             const float* row = qkv + (size_t)(start + t0 + t) * ld;
-            ks[t * D.d + c] = row[k_off + c];
-            qs[t * D.d + c] = row[q_off + c];
+            cp_async4(ks + idx, row + k_off + c);
+            cp_async4(qs + idx, row + q_off + c);
         }
         for (int idx = tid; idx < tt * DR_COLS; idx += blockDim.x) {
             const int t = idx / DR_COLS, c = idx % DR_COLS;
-            vs[idx] = col0 + c < D.dv ? qkv[(size_t)(start + t0 + t) * ld + v_off + col0 + c] : 0.f;
+            if (col0 + c < D.dv) cp_async4(vs + idx, qkv + (size_t)(start + t0 + t) * ld + v_off + col0 + c);
+            else vs[idx] = 0.f;
         }
         if (tid < tt) {
-            bs[tid] = beta[(size_t)(start + t0 + tid) * D.H + h];
-            gs[tid] = decay[(size_t)(start + t0 + tid) * D.H + h];
+            cp_async4(bs + tid, beta + (size_t)(start + t0 + tid) * D.H + h);
+            cp_async4(gs + tid, decay + (size_t)(start + t0 + tid) * D.H + h);
         }
-        __syncthreads();
+        cp_async_commit();
+    };
+    if (len > 0) stage(0, 0);
+    int buf = 0;
+    for (int t0 = 0; t0 < len; t0 += DR_TT, buf ^= 1) {
+        const int tt = len - t0 < DR_TT ? len - t0 : DR_TT;
+        cp_async_wait<0>();
+        __syncthreads();                                      // group t0 landed; everyone is done with the other half
+        if (t0 + DR_TT < len) stage(buf ^ 1, t0 + DR_TT);
+        const float* ks = sm + (size_t)buf * tile_floats;
+        const float* qs = ks + DR_TT * D.d;
+        const float* vs = qs + DR_TT * D.d;
+        const float* bs = vs + DR_TT * DR_COLS;
+        const float* gs = bs + DR_TT;
         for (int t = 0; t < tt; ++t) {
             const float* kt = ks + t * D.d;
             const float* qt = qs + t * D.d;
             const float g = gs[t];
-            float r = 0.f;
+            float r[4] = {0.f, 0.f, 0.f, 0.f};                // four chains: the sum over this thread's rows is not one dependent sequence
 #pragma unroll
             for (int m = 0; m < DPT; ++m) {
                 const int i = p + DR_PARTS * m;
-                if (i < D.d) r = fmaf(s[m], kt[i], r);
+                if (i < D.d) r[m & 3] = fmaf(s[m], kt[i], r[m & 3]);
             }
-            r += __shfl_xor_sync(0xffffffffu, r, 1);
-            r += __shfl_xor_sync(0xffffffffu, r, 2);
-            const float u = bs[t] * (vs[t * DR_COLS + jl] - g * r);
-            float out = 0.f;
+            float rs = (r[0] + r[1]) + (r[2] + r[3]);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+            const float u = bs[t] * (vs[t * DR_COLS + jl] - g * rs);
+            float out[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int m = 0; m < DPT; ++m) {
                 const int i = p + DR_PARTS * m;
                 if (i < D.d) {
                     s[m] = fmaf(kt[i], u, g * s[m]);
-                    out = fmaf(s[m], qt[i], out);
+                    out[m & 3] = fmaf(s[m], qt[i], out[m & 3]);
                 }
             }
-            out += __shfl_xor_sync(0xffffffffu, out, 1);
-            out += __shfl_xor_sync(0xffffffffu, out, 2);
-            if (p == 0 && col_ok) o[((size_t)(start + t0 + t) * D.H + h) * D.dv + col] = out;
+            float os = (out[0] + out[1]) + (out[2] + out[3]);
+            os += __shfl_xor_sync(0xffffffffu, os, 1);
+            os += __shfl_xor_sync(0xffffffffu, os, 2);
+            if (p == 0 && col_ok) o[((size_t)(start + t0 + t) * D.H + h) * D.dv + col] = os;
         }
     }
 #pragma unroll
@@ -140,8 +162,13 @@ int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int 
     if (b.nseq <= 0) return WF_OK;
     if (D.Hk <= 0 || D.H % D.Hk) { set_error("delta: %d heads over %d key heads", D.H, D.Hk); return WF_ERR_INVALID; }
     dim3 grid(b.nseq, D.H, (D.dv + DR_COLS - 1) / DR_COLS);
-    const size_t smem = ((size_t)2 * DR_TT * D.d + DR_TT * DR_COLS + 2 * DR_TT) * sizeof(float);
+    const size_t smem = 2 * ((size_t)2 * DR_TT * D.d + DR_TT * DR_COLS + 2 * DR_TT) * sizeof(float);   // two token groups
     const int threads = DR_COLS * DR_PARTS;
+    static DevOnce once;
+    if (once.need()) {
+        cudaFuncSetAttribute(delta_rule_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(delta_rule_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    }
     const int dpt = (D.d + DR_PARTS - 1) / DR_PARTS;
     if (dpt <= 8) delta_rule_kernel<8><<<grid, threads, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o);
     else if (dpt <= 16) delta_rule_kernel<16><<<grid, threads, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o);
