@@ -847,13 +847,14 @@ def run_hybrid(args):
         ms = m.engine.time_step(slots[:1], [prompt], iters=K)
         res["prefill"] = {"tokens": prompt, "ms": round(ms, 3), "tok_s": round(prompt / ms * 1e3, 1)}
         res["prefill_profile_ms"] = {k: round(v[0], 4) for k, v in m.engine.profile_step(slots[:1], [prompt], iters=2).items()}
-        launches += m.engine.launches_last_step()
+        launches += (K + 2) * m.engine.launches_last_step()
         res["decode"] = {}
         for b, ctx in decode_points:
             for s_ in slots[:b]:
                 m.engine.set_length(s_, ctx)
             ms = m.engine.time_step(slots[:b], [1] * b, iters=max(K, 10))
-            res["decode"][f"bs{b}_ctx{ctx}"] = {"ms": round(ms, 4), "tok_s": round(b / ms * 1e3, 1)}
+            res["decode"][f"bs{b}_ctx{ctx}"] = {"ms": round(ms, 4), "tok_s": round(b / ms * 1e3, 1), "launches_per_step": m.engine.launches_last_step()}
+            launches += (max(K, 10) + 2) * m.engine.launches_last_step()
             if b in (1, 64):
                 res[f"decode_profile_ms_bs{b}"] = {k: round(v[0], 4) for k, v in m.engine.profile_step(slots[:b], [1] * b, iters=3).items()}
         res["weight_bytes_per_token"] = hybrid_layer_bytes(z)

@@ -500,3 +500,73 @@ def test_latent_attention_on_tensor_cores_with_key_splits(heads, kv_rank, rot_di
     err = rel_err(np.concatenate(got), want)
     assert err.max() < TOL["bfloat16"], (int(err.argmax()), err.max())
     m.close()
+
+
+def _write_model_dir(path, cfg, weights):
+    import json
+    import struct
+    header, blob = {}, b""
+    for name, a in weights.items():
+        raw = torch.from_numpy(a).to(torch.bfloat16).view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(a.shape), "data_offsets": [len(blob), len(blob) + len(raw)]}
+        blob += raw
+    h = json.dumps(header).encode()
+    (path / "config.json").write_text(json.dumps(cfg))
+    with open(path / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h + blob)
+
+
+def test_command_line_trace_replay_and_generate(tmp_path):
+    """The two commands on a model folder written here: `trace` (bin/trace_run) replays a schedule with mixed batches, a pause, a
+    finished request whose slot and pages go to the next one; `generate` runs the scheduler.  Both against the oracle."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    cfg = CONFIGS["mixed"]
+    w = make_weights(cfg, 71)
+    _write_model_dir(tmp_path, cfg, w)
+    reqs = {"a": tokens_for(cfg, 21, 72), "b": tokens_for(cfg, 9, 73), "c": tokens_for(cfg, 14, 74)}
+    want = {k: oracle_logits(cfg, w, v) for k, v in reqs.items()}
+    plan = [[("a", 6)], [("a", 1), ("b", 8)], [("a", 10), ("b", 1)], [("a", 4)], [("c", 2)], [("c", 11)], [("c", 1)]]
+    fed, lines, expect = {k: 0 for k in reqs}, [], []
+    for n, step in enumerate(plan):
+        ents, end, rows = [], [], []
+        for rid, c in step:
+            ents.append({"id": rid, "tokens": reqs[rid][fed[rid]:fed[rid] + c], "want": list(range(c))})
+            rows += [(rid, fed[rid] + k) for k in range(c)]
+            fed[rid] += c
+            if fed[rid] == len(reqs[rid]):
+                end.append(rid)
+        lines.append(json.dumps({"step": n, "entries": ents, "end": end}))
+        expect.append(rows)
+    out = tmp_path / "out"
+    out.mkdir()
+    for dtype, tol in (("float32", 2e-4), ("bfloat16", None)):
+        r = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(tmp_path), "--dtype", dtype, "--out", str(out), "--max-tokens", "64", "--slots", "2"],
+                           input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [ln for ln in r.stdout.splitlines() if ln.startswith("done ")] == [f"done {n}" for n in range(len(plan))]
+        for n, rows in enumerate(expect):
+            got = np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(len(rows), cfg["vocab"])
+            ref = np.stack([want[rid][pos] for rid, pos in rows])
+            if tol:
+                assert rel_err(got, ref).max() < tol, (dtype, n)
+            else:
+                assert_close(got, ref, dtype, n)
+    sys.path.insert(0, str(root / "wrinklefree-inference-engine_b200"))
+    r = subprocess.run([sys.executable, "-m", "wf_bitnet.cli", "generate", "--model", str(tmp_path), "--dtype", "float32", "--max-new-tokens", "5",
+                        "--prompt-ids", ",".join(map(str, reqs["a"])), "--prompt-ids", ",".join(map(str, reqs["b"])), "--slots", "1", "--prefill-chunk", "4"],
+                       capture_output=True, text=True, timeout=600, env=dict(__import__("os").environ, PYTHONPATH=str(root / "wrinklefree-inference-engine_b200")))
+    assert r.returncode == 0, r.stderr[-2000:]
+    outs = [json.loads(ln) for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert [o["id"] for o in outs] == ["r0", "r1"]
+    for o, rid in zip(outs, ("a", "b")):
+        seq = list(reqs[rid])
+        for t in o["output_ids"]:
+            lg = oracle_logits(cfg, w, seq)[-1]
+            top2 = np.sort(lg)[-2:]
+            if top2[1] - top2[0] > 1e-3 * np.abs(lg).max():
+                assert int(np.argmax(lg)) == t
+            seq.append(t)

@@ -138,6 +138,16 @@ def test_scheduler_batches_decodes_with_prompt_portions_and_reuses_slots():
         for t in r.output:
             assert t == (len(seq) - 1 + seq[-1]) % m.vocab
             seq.append(t)
+    # a lone request whose prompt takes several steps: steps in which no logits are wanted must still run
+    m1 = FakeModel(slots=1, pages=8, page_size=4, max_step_tokens=8)
+    s1 = Scheduler(m1, max_prefill_chunk=4)
+    s1.add(Request("solo", [5] * 9, max_new_tokens=3))
+    (solo,) = s1.run()
+    assert [c for bt in m1.batches for _, c in bt] == [4, 4, 1, 1, 1]
+    seq = list(solo.prompt)
+    for t in solo.output:
+        assert t == (len(seq) - 1 + seq[-1]) % m1.vocab
+        seq.append(t)
     with pytest.raises(RuntimeError):
         s2 = Scheduler(FakeModel(pages=2))
         s2.add(Request("big", [0] * 20, max_new_tokens=4))

@@ -803,7 +803,9 @@ extern "C" int wf_seq_time_step(wf_seq_engine* e, int nseq, const int32_t* slots
     cudaEventCreate(&e0); cudaEventCreate(&e1);
     for (int it = -2; it < iters; ++it) {      // two untimed passes first (the second one captures the graph of a decode shape)
         if (it == 0) cudaEventRecord(e0, e->stream);
+        const long long l0 = launch_count();
         if ((rc = run_model(e, v, nseq))) break;
+        if (it == -2) e->launches = (int)(launch_count() - l0);      // the eager pass: what one step launches
     }
     cudaEventRecord(e1, e->stream);
     const cudaError_t ce = cudaStreamSynchronize(e->stream);

@@ -144,7 +144,7 @@ class Scheduler:
         order = sorted(range(len(want)), key=lambda k: owners[k].sampling.key())
         want = [want[k] for k in order]
         owners = [owners[k] for k in order]
-        logits = execute(self.model, entries, want, fetch=True) if want else None
+        logits = execute(self.model, entries, want, fetch=True)       # also when nothing is wanted: the portions must run
         self.steps += 1
         finished = []
         if want:
