@@ -54,15 +54,17 @@ def cmd_trace(a) -> int:
             continue
         st = json.loads(line)
         entries, want = [], []
-        for ei, ent in enumerate(st.get("entries", [])):
+        for ent in st.get("entries", []):
             rid = ent["id"]
             if rid not in slot_of:
                 slot = model.admit()
                 if slot < 0:
                     raise RuntimeError(f"no free state slot for request {rid!r}")
                 slot_of[rid] = slot
+            if not ent.get("tokens"):
+                continue                                   # admitted, brings nothing in this step
+            want.extend((len(entries), int(w)) for w in ent.get("want", []))
             entries.append((slot_of[rid], ent["tokens"]))
-            want.extend((ei, int(w)) for w in ent.get("want", []))
         if entries:
             rows = execute(model, entries, want, fetch=True)
             if want:
