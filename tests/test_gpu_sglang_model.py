@@ -150,3 +150,49 @@ def test_fused_qkv_and_mlp_ops_match_the_oracle_step(batch):
     # 1-D input (the reference's bs=1 call shape) and a second call through the cached fused tiles
     q1, _, _ = torch.ops.sgl_kernel.bitnet_qkv_forward_cpu(x[0].cuda(), dev["q"], dev["k"], dev["v"], scales["q"], scales["k"], scales["v"])
     assert q1.shape == (nq,) and torch.equal(q1.cpu(), q[0].cpu())
+
+
+def test_bitnet_through_registry_scheduler_and_command_line(tmp_path):
+    """A BitNet folder (config.json names BitNetForCausalLM) is found by the registry and generates through the scheduler behind the
+    command line: one sequence slot, prompts read token by token, requests served one after another — the same greedy tokens as the
+    engine driven directly."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from safetensors.torch import save_file
+    from test_gpu_loader import _state_dict
+    from wf_bitnet import registry
+    from wf_bitnet.engine import Engine, EngineConfig
+    from wf_bitnet.synth import make_weights
+    root = Path(__file__).resolve().parent.parent
+    cfg = EngineConfig(hidden=256, layers=2, heads=4, kv_heads=2, head_dim=128, ffn=384, vocab=512, max_seq=64, page_size=16, max_batch=1)
+    weights = make_weights(cfg, seed=33, keep_ternary=True)
+    save_file({k: v.contiguous() for k, v in _state_dict(cfg, weights, "hf").items()}, str(tmp_path / "model.safetensors"))
+    hf = {"architectures": ["BitNetForCausalLM"], "hidden_size": 256, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128,
+          "intermediate_size": 384, "vocab_size": 512, "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.eps, "max_position_embeddings": 64}
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    assert registry.resolve(hf).__name__ == "BitNetForCausalLM"
+    prompts = [[5, 77, 300, 9, 41], [17, 2, 250]]
+    want = []
+    eng = Engine(cfg)
+    eng.load_weights(weights)
+    for p in prompts:
+        eng.reset()
+        out = []
+        for t in p:
+            nxt = int(eng.decode([t])[0])
+        for _ in range(4):
+            out.append(nxt)
+            nxt = int(eng.decode([nxt])[0])
+        want.append(out)
+    eng.close()
+    pkg = str(root / "wrinklefree-inference-engine_b200")
+    r = subprocess.run([sys.executable, "-m", "wf_bitnet.cli", "generate", "--model", str(tmp_path), "--max-new-tokens", "4", "--max-tokens", "64", "--slots", "1",
+                        "--prompt-ids", ",".join(map(str, prompts[0])), "--prompt-ids", ",".join(map(str, prompts[1]))],
+                       capture_output=True, text=True, timeout=600, env=dict(os.environ, PYTHONPATH=pkg + os.pathsep + str(root)))
+    assert r.returncode == 0, r.stderr[-2000:]
+    outs = [json.loads(ln) for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert [o["output_ids"] for o in outs] == want

@@ -149,5 +149,75 @@ class BitNetForCausalLM(nn.Module):
     def generate(self, prompt_ids, max_new_tokens: int):
         return self.engine.generate_greedy(list(prompt_ids), max_new_tokens)
 
+    # ---- the step interface of wf_bitnet.scheduler / the command line (admit / release / step / sample) -------------------------------
+    # The decode engine advances its batch slots together, one token per step, so this adapter serves ONE live sequence (slot 0) and
+    # reads a prompt portion token by token; requests queue up behind it in the scheduler.  Sampling is the engine's greedy argmax.
+    architecture_names = ("BitNetForCausalLM", "BitnetForCausalLM")
+    min_page_size = 16
+
+    @classmethod
+    def from_pretrained(cls, model_dir, config=None, *, max_tokens: int = 4096, page_size: int = 16, **_unused):
+        """Model folder (config.json + *.safetensors in any of the loader's forms) -> a model with one sequence slot."""
+        import json
+        from pathlib import Path
+
+        from wf_bitnet import loader
+        cfg = config if config is not None else json.loads((Path(model_dir) / "config.json").read_text())
+        seq = max(page_size, (int(max_tokens) + page_size - 1) // page_size * page_size)
+        m = cls(cfg, max_batch=1, max_seq=seq, page_size=page_size)
+        loader.load_safetensors_dir(m.engine, model_dir)
+        return m
+
+    @property
+    def vocab(self) -> int:
+        return self.engine_config.vocab
+
+    max_step_tokens = 256
+
+    def admit(self) -> int:
+        if getattr(self, "_live", False):
+            return -1
+        self.engine.reset()
+        self._live, self._held = True, 0
+        return 0
+
+    def release(self, slot: int) -> None:
+        self._live, self._held = False, 0
+
+    def free_slots(self) -> int:
+        return 0 if getattr(self, "_live", False) else 1
+
+    def pages_for(self, tokens: int) -> int:
+        ps = self.engine_config.page_size
+        return (tokens + ps - 1) // ps
+
+    def free_pages(self) -> int:
+        return self.engine_config.max_seq // self.engine_config.page_size - self.pages_for(getattr(self, "_held", 0))
+
+    def step(self, slots, counts, tokens, want=(), fetch: bool = True):
+        if list(slots) != [0] or not getattr(self, "_live", False):
+            raise ValueError("the BitNet engine serves one live sequence (slot 0) through this interface")
+        want = list(want)
+        rows = {}
+        for k, t in enumerate(tokens):
+            self.engine.decode([int(t)])
+            self._held += 1
+            if k in want:
+                rows[k] = self.engine.buffer("logits", (1, self.engine_config.vocab), torch.float32)[0].cpu().numpy()
+        self._last_rows = [rows[k] for k in want]
+        if not want or not fetch:
+            return None
+        import numpy as np
+        return np.stack(self._last_rows)
+
+    def sample(self, nrows: int, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, uniforms=None):
+        import numpy as np
+        if temperature > 0:
+            raise NotImplementedError("the BitNet engine samples greedily")
+        return np.array([int(r.argmax()) for r in self._last_rows[:nrows]], dtype=np.int32)
+
+    def close(self) -> None:
+        self.engine.close()
+
 
 EntryClass = BitNetForCausalLM

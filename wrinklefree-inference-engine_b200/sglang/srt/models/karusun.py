@@ -92,6 +92,16 @@ class KarusunForCausalLM:
         self.vocab = c.vocab
         self.max_step_tokens = max_step_tokens
 
+    @classmethod
+    def from_pretrained(cls, model_dir, config=None, **serving):
+        """Model folder (config.json + model.safetensors) -> a loaded model; `serving`: dtype, max_tokens, slots, page_size,
+        max_step_tokens, build."""
+        from pathlib import Path
+        cfg = config if config is not None else checkpoint.read_config(model_dir)
+        m = cls(cfg, **serving)
+        m.load_safetensors(Path(model_dir) / "model.safetensors")
+        return m
+
     # ---- weights
     def load_weights(self, weights: Iterable[Tuple[str, np.ndarray, str]]) -> None:
         """weights: (checkpoint name, array, safetensors dtype string) — bfloat16 as uint16 bit patterns (wf_bitnet.checkpoint)."""

@@ -19,14 +19,13 @@ from . import checkpoint, registry
 
 
 def load_model(model_dir, dtype: str, max_tokens: int, slots: int, page_size: int, max_step_tokens: int):
+    """config.json -> model class (registry) -> a loaded model that implements the step interface."""
     cfg = checkpoint.read_config(model_dir)
     cls = registry.resolve(cfg)
-    if not hasattr(cls, "step"):
-        raise SystemExit(f"{cls.__name__} does not implement the ragged step interface this command drives")
-    model = cls(cfg, dtype=dtype, max_tokens=max_tokens, slots=slots, page_size=max(page_size, getattr(cls, "min_page_size", 1)),
-                max_step_tokens=max_step_tokens, build=True)
-    model.load_safetensors(Path(model_dir) / "model.safetensors")
-    return model
+    if not hasattr(cls, "step") or not hasattr(cls, "from_pretrained"):
+        raise SystemExit(f"{cls.__name__} does not implement the step interface this command drives")
+    return cls.from_pretrained(model_dir, cfg, dtype=dtype, max_tokens=max_tokens, slots=slots, page_size=max(page_size, getattr(cls, "min_page_size", 1)),
+                               max_step_tokens=max_step_tokens, build=True)
 
 
 def cmd_generate(a) -> int:
