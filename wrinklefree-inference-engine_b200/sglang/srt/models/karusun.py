@@ -28,12 +28,13 @@ class KarusunConfig:
     norm_groups: int
     canon_taps: int
     layers: List[dict] = field(default_factory=list)
+    has_canon: bool = True
 
     @staticmethod
     def from_dict(cfg: Dict) -> "KarusunConfig":
         norm = cfg.get("norm", {})
         out = KarusunConfig(vocab=int(cfg["vocab"]), width=int(cfg["width"]), eps=float(norm.get("eps", 1e-6)), norm_groups=int(norm.get("groups", 1)),
-                            canon_taps=int(cfg.get("canon", {}).get("taps", 1)), layers=list(cfg["layers"]))
+                            canon_taps=int((cfg.get("canon") or {}).get("taps", 1)), layers=list(cfg["layers"]), has_canon=bool(cfg.get("canon")))
         if not out.layers:
             raise ValueError("config: 'layers' is empty")
         return out
@@ -110,6 +111,10 @@ class KarusunForCausalLM:
             if name not in wanted:
                 continue
             self.engine.set_tensor(name, checkpoint.to_float32(a, dt) if self.dtype == "float32" else checkpoint.to_bfloat16_bits(a, dt))
+        # tensors of parts the configuration does not mention are neutral: no input convolution (zero taps), no choice correction
+        for n, count, loaded in self.engine.expected_tensors():
+            if not loaded and ((not self.config.has_canon and n.endswith((".canon1", ".canon2"))) or n.endswith(".mlp.correction")):
+                self.engine.set_tensor(n, np.zeros(count, dtype=np.float32 if self.dtype == "float32" else np.uint16))
         missing = [n for n, _, loaded in self.engine.expected_tensors() if not loaded]
         if missing:
             raise KeyError(f"checkpoint lacks {len(missing)} tensors, first: {missing[:4]}")
