@@ -30,19 +30,22 @@ __global__ void delta_prep_kernel(DeltaDims D, float* __restrict__ qkv, int ld, 
     }
 }
 
-constexpr int DR_COLS = 32, DR_PARTS = 4, DR_TT = 16;
+constexpr int DR_THREADS = 128, DR_TT = 16;
 
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
 
-// block = (sequence, head, 32 value columns); thread = (column, quarter of the key rows), its part of the column in registers.
+// block = (sequence, head, 16 value columns); thread = (column, eighth of the key rows), its part of the column in registers.
 // Tokens are taken 16 at a time: the next group's k / q / v / gates are copied into the other half of shared memory (cp.async)
 // while the current group runs, so the per-token chain is only register math, shared-memory broadcasts and two quad reductions.
-template <int DPT>
-__global__ void __launch_bounds__(DR_COLS * DR_PARTS) delta_rule_kernel(Batch b, DeltaDims D, const float* __restrict__ qkv, int ld,
+// DR_PARTS = 8 (16 columns per block): short per-token chains and twice the blocks, for portions of many tokens;
+// DR_PARTS = 4 (32 columns): wider, better coalesced state rows, for single decoded tokens where the state traffic is the cost.
+template <int DPT, int DR_PARTS>
+__global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDims D, const float* __restrict__ qkv, int ld,
                                                                          const float* __restrict__ beta, const float* __restrict__ decay,
                                                                          float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
+    constexpr int DR_COLS = DR_THREADS / DR_PARTS;
     extern __shared__ float sm[];
     const int tile_floats = 2 * DR_TT * D.d + DR_TT * DR_COLS + 2 * DR_TT;   // k [TT][d], q [TT][d], v [TT][32], beta [TT], decay [TT]
     const int sq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
@@ -107,6 +110,7 @@ __global__ void __launch_bounds__(DR_COLS * DR_PARTS) delta_rule_kernel(Batch b,
             float rs = (r[0] + r[1]) + (r[2] + r[3]);
             rs += __shfl_xor_sync(0xffffffffu, rs, 1);
             rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+            if (DR_PARTS == 8) rs += __shfl_xor_sync(0xffffffffu, rs, 4);
             const float u = bs[t] * (vs[t * DR_COLS + jl] - g * rs);
             float out[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -120,6 +124,7 @@ __global__ void __launch_bounds__(DR_COLS * DR_PARTS) delta_rule_kernel(Batch b,
             float os = (out[0] + out[1]) + (out[2] + out[3]);
             os += __shfl_xor_sync(0xffffffffu, os, 1);
             os += __shfl_xor_sync(0xffffffffu, os, 2);
+            if (DR_PARTS == 8) os += __shfl_xor_sync(0xffffffffu, os, 4);
             if (p == 0 && col_ok) o[((size_t)(start + t0 + t) * D.H + h) * D.dv + col] = os;
         }
     }
@@ -161,20 +166,23 @@ int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int 
                       size_t slot_stride, float* o, cudaStream_t s) {
     if (b.nseq <= 0) return WF_OK;
     if (D.Hk <= 0 || D.H % D.Hk) { set_error("delta: %d heads over %d key heads", D.H, D.Hk); return WF_ERR_INVALID; }
-    dim3 grid(b.nseq, D.H, (D.dv + DR_COLS - 1) / DR_COLS);
-    const size_t smem = 2 * ((size_t)2 * DR_TT * D.d + DR_TT * DR_COLS + 2 * DR_TT) * sizeof(float);   // two token groups
-    const int threads = DR_COLS * DR_PARTS;
+    const bool decode = b.n == b.nseq;                     // every sequence brings one token
+    const int parts = decode ? 4 : 8, cols = DR_THREADS / parts;
+    dim3 grid(b.nseq, D.H, (D.dv + cols - 1) / cols);
+    const size_t smem = 2 * ((size_t)2 * DR_TT * D.d + DR_TT * cols + 2 * DR_TT) * sizeof(float);   // two token groups
     static DevOnce once;
     if (once.need()) {
-        cudaFuncSetAttribute(delta_rule_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(delta_rule_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(delta_rule_kernel<32, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(delta_rule_kernel<64, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(delta_rule_kernel<32, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(delta_rule_kernel<64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     }
-    const int dpt = (D.d + DR_PARTS - 1) / DR_PARTS;
-    if (dpt <= 8) delta_rule_kernel<8><<<grid, threads, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o);
-    else if (dpt <= 16) delta_rule_kernel<16><<<grid, threads, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o);
-    else if (dpt <= 32) delta_rule_kernel<32><<<grid, threads, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o);
-    else if (dpt <= 64) delta_rule_kernel<64><<<grid, threads, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o);
-    else { set_error("delta: key dimension %d above the supported 256", D.d); return WF_ERR_UNSUPPORTED; }
+    const int dpt = (D.d + parts - 1) / parts;
+#define DR_LAUNCH(dp, pa) delta_rule_kernel<dp, pa><<<grid, DR_THREADS, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o)
+    if (D.d > 256 || smem > 96 * 1024) { set_error("delta: key dimension %d above the supported 256", D.d); return WF_ERR_UNSUPPORTED; }
+    if (decode) { if (dpt <= 8) DR_LAUNCH(8, 4); else if (dpt <= 16) DR_LAUNCH(16, 4); else if (dpt <= 32) DR_LAUNCH(32, 4); else DR_LAUNCH(64, 4); }
+    else { if (dpt <= 8) DR_LAUNCH(8, 8); else if (dpt <= 16) DR_LAUNCH(16, 8); else if (dpt <= 32) DR_LAUNCH(32, 8); else DR_LAUNCH(64, 8); }
+#undef DR_LAUNCH
     return launch_check(cudaGetLastError(), "delta_rule");
 }
 
