@@ -74,6 +74,7 @@ struct wf_seq_engine {
     int P = 0;                        // padded expert-row bound
     int fuse_input = 1;               // norm + input convolution (+ state roll of single-token sequences) in one kernel (WF_SEQ_FUSE_INPUT=0: three kernels)
     int attn_mma = 2;                 // latent attention on tensor cores where the sizes allow it: 2 keys-as-rows form first, 1 heads-as-rows form only, 0 plain kernel (WF_SEQ_ATTN_MMA)
+    float* row_inv = nullptr;         // [max_step_tokens][norm groups] row statistics of the many-token input kernel
     float* attn_ws = nullptr;         // partial results of key-split attention
     int attn_ws_rows = 0;             // token-splits it holds
     int pair_path_max = 64;           // up to this many (token, expert) pairs the experts run as per-pair weight streams (WF_SEQ_PAIR_MAX)
@@ -359,7 +360,12 @@ int run_input(wf_seq_engine* e, const Batch& b, const void* norm_w, const void* 
     const int W = e->cfg.width;
     cudaStream_t s = e->stream;
     int rc;
-    if (e->fuse_input && norm_taps_usable(e->cfg.norm_groups, e->cfg.canon_taps, W)) {
+    if (e->fuse_input && b.n >= 64) {
+        // many tokens: per-row statistics once, then a fully parallel apply (the one-block-per-token kernel recomputes them per tap)
+        if ((rc = launch_norm_taps_rows(e->dt, b, e->x, W, norm_w, e->cfg.norm_groups, e->cfg.eps, canon_w, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride,
+                                        e->h_t, W, e->hn, e->row_inv, s))) return rc;
+        rc = launch_taps_state(b, e->hn, W, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, s);
+    } else if (e->fuse_input && norm_taps_usable(e->cfg.norm_groups, e->cfg.canon_taps, W)) {
         if ((rc = launch_norm_taps(e->dt, b, e->x, W, norm_w, e->cfg.norm_groups, e->cfg.eps, canon_w, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride,
                                    e->h_t, W, e->hn, s))) return rc;
         rc = b.n == b.nseq ? WF_OK : launch_taps_state(b, e->hn, W, e->cfg.canon_taps, W, e->state + st_off, e->slot_stride, s, 1);
@@ -578,6 +584,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     TRY(dalloc_n(e, &e->d_meta, e->meta_ints));
     if (cuda_check(cudaMallocHost((void**)&e->h_meta, e->meta_ints * 4), "pinned metadata")) { wf_seq_destroy(e); return WF_ERR_CUDA; }
     // workspaces
+    TRY(dalloc_n(e, &e->row_inv, (size_t)T * c.norm_groups));
     TRY(dalloc_n(e, &e->x, (size_t)T * W)); TRY(dalloc_n(e, &e->hn, (size_t)T * W)); TRY(dalloc_n(e, &e->y, (size_t)T * W));
     TRY(dalloc_t(e, &e->h_t, (size_t)T * W)); TRY(dalloc_t(e, &e->xn, (size_t)T * W));
     TRY(dalloc_n(e, &e->proj, (size_t)T * max_np));

@@ -25,6 +25,10 @@ int launch_taps_state(const Batch& b, const float* in, int ld_in, int taps, int 
 // hn (float [n, W]) receives the normalised rows of each portion's last taps - 1 tokens, for launch_taps_state(..., skip_single = 1)
 // afterwards; sequences that bring one token have their state rolled here.
 inline bool norm_taps_usable(int groups, int taps, int W) { return groups >= 1 && groups <= 32 && taps >= 1 && taps <= 8 && W % groups == 0; }
+// the form for many tokens: row statistics first (inv: float [n, groups] scratch), then one thread per (token, channel); no state is
+// rolled here (launch_taps_state without skip_single afterwards)
+int launch_norm_taps_rows(int dt, const Batch& b, const float* x, int ldx, const void* nw, int groups, float eps, const void* cw, int taps, int W,
+                          const float* state, size_t slot_stride, void* out_t, int ld_t, float* hn, float* inv, cudaStream_t s);
 int launch_norm_taps(int dt, const Batch& b, const float* x, int ldx, const void* nw, int groups, float eps, const void* cw, int taps, int W, float* state,
                      size_t slot_stride, void* out_t, int ld_t, float* hn, cudaStream_t s);
 

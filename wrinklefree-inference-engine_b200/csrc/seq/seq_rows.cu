@@ -182,6 +182,58 @@ int launch_norm_taps(int dt, const Batch& b, const float* x, int ldx, const void
     return launch_check(cudaGetLastError(), "norm_taps");
 }
 
+// ---- the same for many tokens: statistics once per row, then a fully parallel apply ------------------------------------------------
+// inv[row][group] = 1 / sqrt(mean_group(x^2) + eps): one warp per (row, group)
+__global__ void row_group_inv_rms_kernel(const float* __restrict__ x, int ldx, int n, int groups, int gw, float eps, float* __restrict__ inv) {
+    const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (wid >= n * groups) return;
+    const int row = wid / groups, g = wid - row * groups;
+    const float* p = x + (size_t)row * ldx + (size_t)g * gw;
+    float ss = 0.f;
+    for (int c = lane; c < gw; c += 32) { const float v = p[c]; ss += v * v; }
+    ss = warp_sum(ss);
+    if (lane == 0) inv[wid] = 1.f / sqrtf(ss / (float)gw + eps);
+}
+
+// thread per (token, channel): the taps over rows normalised with the precomputed statistics (or taken from the carried state)
+template <typename T>
+__global__ void norm_taps_apply_kernel(Batch b, const float* __restrict__ x, int ldx, const float* __restrict__ inv, const T* __restrict__ nw, int groups,
+                                       const T* __restrict__ cw, int taps, int W, const float* __restrict__ state, size_t slot_stride, T* __restrict__ out_t,
+                                       int ld_t, float* __restrict__ hn) {
+    const int i = blockIdx.x;
+    const int sq = b.tok_seq[i];
+    const int li = i - b.seq_start[sq], len = b.seq_len[sq];
+    const int gw = W / groups;
+    const float* st = state + (size_t)b.seq_slot[sq] * slot_stride;
+    const bool keep = li >= len - (taps - 1);
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
+        const int g = c / gw;
+        const float wn = to_f(nw[c]);
+        float acc = 0.f, cur = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = li - (taps - 1) + j;
+            const float v = src >= 0 ? x[(size_t)(i - li + src) * ldx + c] * inv[(size_t)(i - li + src) * groups + g] * wn : st[(size_t)(src + taps - 1) * W + c];
+            acc = fmaf(to_f(cw[(size_t)c * taps + j]), v, acc);
+            cur = v;
+        }
+        out_t[(size_t)i * ld_t + c] = from_f<T>(cur + acc);
+        if (keep && hn) hn[(size_t)i * W + c] = cur;
+    }
+}
+
+int launch_norm_taps_rows(int dt, const Batch& b, const float* x, int ldx, const void* nw, int groups, float eps, const void* cw, int taps, int W,
+                          const float* state, size_t slot_stride, void* out_t, int ld_t, float* hn, float* inv, cudaStream_t s) {
+    if (b.n <= 0) return WF_OK;
+    if (groups < 1 || W % groups || taps < 1) { set_error("norm_taps_rows: %d groups / %d taps", groups, taps); return WF_ERR_INVALID; }
+    const int warps = b.n * groups;
+    row_group_inv_rms_kernel<<<(warps + 7) / 8, 256, 0, s>>>(x, ldx, b.n, groups, W / groups, eps, inv);
+    if (int rc = launch_check(cudaGetLastError(), "row_group_inv_rms")) return rc;
+    dim3 grid(b.n, (W + 1023) / 1024);
+    if (dt == WF_BF16) norm_taps_apply_kernel<<<grid, 256, 0, s>>>(b, x, ldx, inv, (const __nv_bfloat16*)nw, groups, (const __nv_bfloat16*)cw, taps, W, state, slot_stride, (__nv_bfloat16*)out_t, ld_t, hn);
+    else norm_taps_apply_kernel<<<grid, 256, 0, s>>>(b, x, ldx, inv, (const float*)nw, groups, (const float*)cw, taps, W, state, slot_stride, (float*)out_t, ld_t, hn);
+    return launch_check(cudaGetLastError(), "norm_taps_apply");
+}
+
 template <typename T>
 __global__ void gate_mul_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ g, int ldg, int act, int C, T* __restrict__ y, int ldy) {
     const int i = blockIdx.x;
