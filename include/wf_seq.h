@@ -79,8 +79,9 @@ int wf_seq_launches_last_step(const wf_seq_engine* e);
 int wf_seq_set_layer_tap(wf_seq_engine* e, float* host);
 int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, const int32_t* slots, const int32_t* counts, const float* in_host,
                     float* out_host);
-/* mean device time of one step shape (measurement): runs the step `iters` times on synthetic tokens, keeps none of them, and returns
- * milliseconds per step */
+/* mean device time of one step shape (measurement): runs the step `iters` times on synthetic tokens and returns milliseconds per step.
+ * Sequence lengths and pages are left as they were; the slots' convolution tails and recurrent state ARE advanced by the timed tokens,
+ * so the slots are not to be used for real requests afterwards without a release / admit. */
 int wf_seq_time_step(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t* counts, int iters, float* ms_out);
 /* the same, with an event after every launch group: out receives JSON {"kind": [ms per step, launches per step], ...} */
 int wf_seq_profile_step(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t* counts, int iters, char* out, size_t cap);
