@@ -195,8 +195,9 @@ __global__ void row_group_inv_rms_kernel(const float* __restrict__ x, int ldx, i
     if (lane == 0) inv[wid] = 1.f / sqrtf(ss / (float)gw + eps);
 }
 
-// thread per (token, channel): the taps over rows normalised with the precomputed statistics (or taken from the carried state)
-template <typename T>
+// thread per (token, 4 channels): the taps over rows normalised with the precomputed statistics (or taken from the carried state).
+// VEC = 4 needs W, the group width and the row strides to be multiples of 4 (one group per thread, 16-byte loads); VEC = 1 takes anything.
+template <typename T, int VEC>
 __global__ void norm_taps_apply_kernel(Batch b, const float* __restrict__ x, int ldx, const float* __restrict__ inv, const T* __restrict__ nw, int groups,
                                        const T* __restrict__ cw, int taps, int W, const float* __restrict__ state, size_t slot_stride, T* __restrict__ out_t,
                                        int ld_t, float* __restrict__ hn) {
@@ -206,18 +207,34 @@ __global__ void norm_taps_apply_kernel(Batch b, const float* __restrict__ x, int
     const int gw = W / groups;
     const float* st = state + (size_t)b.seq_slot[sq] * slot_stride;
     const bool keep = li >= len - (taps - 1);
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC; c < W; c += gridDim.y * blockDim.x * VEC) {
         const int g = c / gw;
-        const float wn = to_f(nw[c]);
-        float acc = 0.f, cur = 0.f;
+        float wn[VEC], acc[VEC], cur[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) { wn[v] = to_f(nw[c + v]); acc[v] = 0.f; cur[v] = 0.f; }
         for (int j = 0; j < taps; ++j) {
             const int src = li - (taps - 1) + j;
-            const float v = src >= 0 ? x[(size_t)(i - li + src) * ldx + c] * inv[(size_t)(i - li + src) * groups + g] * wn : st[(size_t)(src + taps - 1) * W + c];
-            acc = fmaf(to_f(cw[(size_t)c * taps + j]), v, acc);
-            cur = v;
+            float val[VEC];
+            if (src >= 0) {
+                const float* xr = x + (size_t)(i - li + src) * ldx + c;
+                const float iv = inv[(size_t)(i - li + src) * groups + g];
+                if (VEC == 4) { const float4 q = *reinterpret_cast<const float4*>(xr); val[0] = q.x; val[1 % VEC] = q.y; val[2 % VEC] = q.z; val[3 % VEC] = q.w; }
+                else val[0] = xr[0];
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) val[v] *= iv * wn[v];
+            } else {
+                const float* sr = st + (size_t)(src + taps - 1) * W + c;
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) val[v] = sr[v];
+            }
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) { acc[v] = fmaf(to_f(cw[(size_t)(c + v) * taps + j]), val[v], acc[v]); cur[v] = val[v]; }
         }
-        out_t[(size_t)i * ld_t + c] = from_f<T>(cur + acc);
-        if (keep && hn) hn[(size_t)i * W + c] = cur;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            out_t[(size_t)i * ld_t + c + v] = from_f<T>(cur[v] + acc[v]);
+            if (keep && hn) hn[(size_t)i * W + c + v] = cur[v];
+        }
     }
 }
 
@@ -228,9 +245,15 @@ int launch_norm_taps_rows(int dt, const Batch& b, const float* x, int ldx, const
     const int warps = b.n * groups;
     row_group_inv_rms_kernel<<<(warps + 7) / 8, 256, 0, s>>>(x, ldx, b.n, groups, W / groups, eps, inv);
     if (int rc = launch_check(cudaGetLastError(), "row_group_inv_rms")) return rc;
-    dim3 grid(b.n, (W + 1023) / 1024);
-    if (dt == WF_BF16) norm_taps_apply_kernel<<<grid, 256, 0, s>>>(b, x, ldx, inv, (const __nv_bfloat16*)nw, groups, (const __nv_bfloat16*)cw, taps, W, state, slot_stride, (__nv_bfloat16*)out_t, ld_t, hn);
-    else norm_taps_apply_kernel<<<grid, 256, 0, s>>>(b, x, ldx, inv, (const float*)nw, groups, (const float*)cw, taps, W, state, slot_stride, (float*)out_t, ld_t, hn);
+    const bool vec = W % 4 == 0 && (W / groups) % 4 == 0 && ldx % 4 == 0 && (((uintptr_t)x) & 15) == 0;
+    dim3 grid(b.n, vec ? (W + 1023) / 1024 : (W + 255) / 256);
+    if (dt == WF_BF16) {
+        if (vec) norm_taps_apply_kernel<__nv_bfloat16, 4><<<grid, 256, 0, s>>>(b, x, ldx, inv, (const __nv_bfloat16*)nw, groups, (const __nv_bfloat16*)cw, taps, W, state, slot_stride, (__nv_bfloat16*)out_t, ld_t, hn);
+        else norm_taps_apply_kernel<__nv_bfloat16, 1><<<grid, 256, 0, s>>>(b, x, ldx, inv, (const __nv_bfloat16*)nw, groups, (const __nv_bfloat16*)cw, taps, W, state, slot_stride, (__nv_bfloat16*)out_t, ld_t, hn);
+    } else {
+        if (vec) norm_taps_apply_kernel<float, 4><<<grid, 256, 0, s>>>(b, x, ldx, inv, (const float*)nw, groups, (const float*)cw, taps, W, state, slot_stride, (float*)out_t, ld_t, hn);
+        else norm_taps_apply_kernel<float, 1><<<grid, 256, 0, s>>>(b, x, ldx, inv, (const float*)nw, groups, (const float*)cw, taps, W, state, slot_stride, (float*)out_t, ld_t, hn);
+    }
     return launch_check(cudaGetLastError(), "norm_taps_apply");
 }
 
