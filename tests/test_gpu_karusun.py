@@ -570,3 +570,31 @@ def test_command_line_trace_replay_and_generate(tmp_path):
             if top2[1] - top2[0] > 1e-3 * np.abs(lg).max():
                 assert int(np.argmax(lg)) == t
             seq.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_delta_rule_long_memory_across_portions(dtype):
+    """Decay made almost 1 (large negative A_log and dt_bias): what a token wrote 300 tokens ago is still read, so a state that is lost,
+    zeroed or carried in the wrong slot at any portion border changes every later output — with quick decay it would fade unnoticed."""
+    cfg = config([delta(heads=4, kv_heads=2, dim=24, vdim=40, conv=4)], width=64, vocab=40, groups=1, taps=1)
+    w = make_weights(cfg, 81)
+    w["l0.mix.A_log"] = bf16_exact(np.full(4, -8.0))
+    w["l0.mix.dt_bias"] = bf16_exact(np.full(4, -4.0))
+    m = build(cfg, w, dtype, max_tokens=512, slots=2, page_size=16, max_step_tokens=160)
+    n = 300
+    x = _rows(n, 64, 82)
+    P = {k: torch.from_numpy(v).double() for k, v in O.sub(w, "l0.mix.").items()}
+    want = O.gated_delta(torch.from_numpy(x).double(), P, cfg["layers"][0]["mixer"], 1e-6).numpy()
+    # sensitivity of the oracle itself: forgetting the first 150 tokens moves the last outputs far beyond the tolerance
+    late = O.gated_delta(torch.from_numpy(x[150:]).double(), P, cfg["layers"][0]["mixer"], 1e-6).numpy()
+    assert rel_err(late[-20:], want[-20:]).min() > 0.1
+    other = m.admit()                                            # a neighbour in the other slot, stepped in between
+    s = m.admit()
+    got, a = [], 0
+    for c in (128, 3, 2, 1, 1, 100, 65):
+        got.append(m.engine.run_part(0, 2, [s], [c], x[a:a + c]))
+        m.engine.run_part(0, 2, [other], [2], _rows(2, 64, 83 + a))
+        a += c
+    err = rel_err(np.concatenate(got), want)
+    assert err.max() < (1e-3 if dtype == "float32" else TOL[dtype]), (int(err.argmax()), err.max())
+    m.close()
