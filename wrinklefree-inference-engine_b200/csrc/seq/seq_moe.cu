@@ -95,28 +95,51 @@ __global__ void moe_plan_kernel(RouterDims R, int n, const int32_t* __restrict__
     }
 }
 
-template <typename T>
+// VEC = 4: ff a multiple of 4 (16-byte loads of the gate and up halves)
+template <typename T, int VEC>
 __global__ void silu_mul_kernel(const float* __restrict__ gu, int ff, const int32_t* __restrict__ tile_group, T* __restrict__ hmid) {
     const int r = blockIdx.x;
     if (tile_group && tile_group[r / GEMM_BM] < 0) return;
     const float* row = gu + (size_t)r * 2 * ff;
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ff; c += gridDim.y * blockDim.x) hmid[(size_t)r * ff + c] = from_f<T>(silu_f(row[c]) * row[ff + c]);
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC; c < ff; c += gridDim.y * blockDim.x * VEC) {
+        float g[VEC], u[VEC];
+        if (VEC == 4) {
+            const float4 a = *reinterpret_cast<const float4*>(row + c), b = *reinterpret_cast<const float4*>(row + ff + c);
+            g[0] = a.x; g[1 % VEC] = a.y; g[2 % VEC] = a.z; g[3 % VEC] = a.w;
+            u[0] = b.x; u[1 % VEC] = b.y; u[2 % VEC] = b.z; u[3 % VEC] = b.w;
+        } else { g[0] = row[c]; u[0] = row[ff + c]; }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) hmid[(size_t)r * ff + c + v] = from_f<T>(silu_f(g[v]) * u[v]);
+    }
 }
 
-template <typename T>
+// VEC = 4: W a multiple of 4
+template <typename T, int VEC>
 __global__ void moe_combine_kernel(RouterDims R, int W, const int32_t* __restrict__ ids, const float* __restrict__ wts, const int32_t* __restrict__ pair_row,
                                    const float* __restrict__ y, const T* __restrict__ h, float* __restrict__ out) {
     const int i = blockIdx.x;
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
-        float acc = 0.f;
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC; c < W; c += gridDim.y * blockDim.x * VEC) {
+        float acc[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
         for (int k = 0; k < R.top; ++k) {
-            const int e = ids[(size_t)i * R.top + k];
-            const float w = wts[(size_t)i * R.top + k];
             const size_t pi = (size_t)i * R.top + k;
-            const float v = e < R.E ? y[(size_t)(pair_row ? pair_row[pi] : (int)pi) * W + c] : to_f(h[(size_t)i * W + c]);
-            acc = fmaf(w, v, acc);
+            const int e = ids[pi];
+            const float w = wts[pi];
+            float val[VEC];
+            if (e < R.E) {
+                const float* yr = y + (size_t)(pair_row ? pair_row[pi] : (int)pi) * W + c;
+                if (VEC == 4) { const float4 q = *reinterpret_cast<const float4*>(yr); val[0] = q.x; val[1 % VEC] = q.y; val[2 % VEC] = q.z; val[3 % VEC] = q.w; }
+                else val[0] = yr[0];
+            } else {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) val[v] = to_f(h[(size_t)i * W + c + v]);
+            }
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] = fmaf(w, val[v], acc[v]);
         }
-        out[(size_t)i * W + c] = acc;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) out[(size_t)i * W + c + v] = acc[v];
     }
 }
 
@@ -147,18 +170,22 @@ int launch_moe_plan(const RouterDims& R, int n, const int32_t* ids, const int32_
 
 int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s) {
     if (P <= 0) return WF_OK;
-    const dim3 grid(P, P < 256 ? (ff + 127) / 128 : 1);
-    if (dt == WF_BF16) silu_mul_kernel<<<grid, 128, 0, s>>>(gu, ff, tile_group, (__nv_bfloat16*)hmid);
-    else silu_mul_kernel<<<grid, 128, 0, s>>>(gu, ff, tile_group, (float*)hmid);
+    const bool vec = ff % 4 == 0 && (((uintptr_t)gu) & 15) == 0;
+    const int per = 128 * (vec ? 4 : 1);
+    const dim3 grid(P, P < 256 ? (ff + per - 1) / per : 1);
+    if (dt == WF_BF16) { if (vec) silu_mul_kernel<__nv_bfloat16, 4><<<grid, 128, 0, s>>>(gu, ff, tile_group, (__nv_bfloat16*)hmid); else silu_mul_kernel<__nv_bfloat16, 1><<<grid, 128, 0, s>>>(gu, ff, tile_group, (__nv_bfloat16*)hmid); }
+    else { if (vec) silu_mul_kernel<float, 4><<<grid, 128, 0, s>>>(gu, ff, tile_group, (float*)hmid); else silu_mul_kernel<float, 1><<<grid, 128, 0, s>>>(gu, ff, tile_group, (float*)hmid); }
     return launch_check(cudaGetLastError(), "silu_mul");
 }
 
 int launch_moe_combine(int dt, const RouterDims& R, int n, int W, const int32_t* ids, const float* wts, const int32_t* pair_row, const float* y,
                        const void* h, float* out, cudaStream_t s) {
     if (n <= 0) return WF_OK;
-    const dim3 grid(n, n < 64 ? (W + 255) / 256 : 1);       // few tokens: spread a row over several blocks
-    if (dt == WF_BF16) moe_combine_kernel<<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const __nv_bfloat16*)h, out);
-    else moe_combine_kernel<<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const float*)h, out);
+    const bool vec = W % 4 == 0 && (((uintptr_t)y) & 15) == 0 && (((uintptr_t)out) & 15) == 0;
+    const int per = 256 * (vec ? 4 : 1);
+    const dim3 grid(n, n < 64 ? (W + per - 1) / per : 1);       // few tokens: spread a row over several blocks
+    if (dt == WF_BF16) { if (vec) moe_combine_kernel<__nv_bfloat16, 4><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const __nv_bfloat16*)h, out); else moe_combine_kernel<__nv_bfloat16, 1><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const __nv_bfloat16*)h, out); }
+    else { if (vec) moe_combine_kernel<float, 4><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const float*)h, out); else moe_combine_kernel<float, 1><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const float*)h, out); }
     return launch_check(cudaGetLastError(), "moe_combine");
 }
 
