@@ -480,7 +480,7 @@ def test_grouped_matrix_product_on_the_tensor_cores():
                 assert (got[rows].double() - want).abs().max() < 2e-3 * (1 + want.abs().max()), (algo, t)
 
 
-@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(20, 128, 16), (5, 512, 32), (33, 256, 8)])
+@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(20, 128, 16), (5, 512, 32), (33, 256, 8), (7, 80, 24), (32, 48, 0)])
 def test_latent_attention_on_tensor_cores_with_key_splits(heads, kv_rank, rot_dim):
     """Sizes that take the tensor-core attention kernel (latent a multiple of 32): padded head tiles, several head tiles, and a window
     long enough that single decoded tokens have their keys split over several CTAs and merged."""

@@ -313,15 +313,17 @@ int run_ff(wf_seq_engine* e, LayerState& L, const Batch& b) {
     RouterDims R{c.experts, c.identity, c.top, c.groups, c.keep};
     if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.router, W, e->z, 1, N, n, N, W), s))) return rc;
     mark(e, "moe.router");
-    if (c.experts > 0 && cuda_check(cudaMemsetAsync(e->counts, 0, (size_t)c.experts * 4, s), "counts")) return WF_ERR_CUDA;
-    if ((rc = launch_moe_route(e->dt, R, n, e->z, N, L.correction, e->ids, e->wts, e->counts, s))) return rc;
-    mark(e, "moe.router");
     const int pairs = n * c.top;
     GemmArgs gp = lin(e->h_t, 0, W, L.wgu, W, e->gu, 1, 2 * c.ff, pairs, 2 * c.ff, W);
     gp.group_stride = (long long)2 * c.ff * W;
     GemmArgs gd = lin(e->hmid, 0, c.ff, L.wd, c.ff, e->yexp, 1, W, pairs, W, c.ff);
     gd.group_stride = (long long)W * c.ff;
-    if (c.experts > 0 && pairs <= e->pair_path_max && gemv_pairs_usable(e->dt, gp) && gemv_pairs_usable(e->dt, gd)) {
+    const bool pair_path = c.experts > 0 && pairs <= e->pair_path_max && gemv_pairs_usable(e->dt, gp) && gemv_pairs_usable(e->dt, gd);
+    // per-expert token counts are only needed to sort the pairs (the per-pair path sorts nothing)
+    if (c.experts > 0 && !pair_path && cuda_check(cudaMemsetAsync(e->counts, 0, (size_t)c.experts * 4, s), "counts")) return WF_ERR_CUDA;
+    if ((rc = launch_moe_route(e->dt, R, n, e->z, N, L.correction, e->ids, e->wts, pair_path ? nullptr : e->counts, s))) return rc;
+    mark(e, "moe.router");
+    if (pair_path) {
         // few tokens (decoding): one weight-streaming product per (token, expert) pair, no sorting
         if ((rc = launch_gemv_pairs(e->dt, gp, e->ids, c.experts, pairs, c.top, s))) return rc;
         mark(e, "moe.gate_up");

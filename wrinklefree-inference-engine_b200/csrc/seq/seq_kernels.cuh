@@ -106,7 +106,7 @@ int launch_delta_post(int dt, const DeltaDims& D, int n, const float* o, const v
 
 // ---- routed feed-forward ---------------------------------------------------------------------------------------------------
 struct RouterDims { int E, I, top, groups, keep; };   // E real experts, I identity experts (indices E .. E + I - 1)
-// z float [n, E + I] (ldz) -> ids [n, top], wts [n, top]; counts[E] += tokens per real expert (counts must be zero on entry)
+// z float [n, E + I] (ldz) -> ids [n, top], wts [n, top]; counts[E] += tokens per real expert (zero on entry; null: not counted)
 int launch_moe_route(int dt, const RouterDims& R, int n, const float* z, int ldz, const void* correction, int32_t* ids, float* wts,
                      int32_t* counts, cudaStream_t s);
 // from counts: expert segments padded to GEMM_BM rows.  sorted_rows[P] = token of the row or -1; pair_row[n * top] = row of the pair or -1

@@ -65,7 +65,7 @@ __global__ void moe_route_kernel(RouterDims R, const float* __restrict__ z, int 
             ids[(size_t)i * R.top + k] = ei;
             wts[(size_t)i * R.top + k] = sc[ei];
             ch[ei] = NAN;                                   // taken
-            if (ei < R.E) atomicAdd(&counts[ei], 1);
+            if (counts && ei < R.E) atomicAdd(&counts[ei], 1);
         }
         __syncwarp();
     }
