@@ -197,9 +197,9 @@ __global__ void __launch_bounds__(tc_threads(NU), 1) ternary_gemm_tc_kernel(cons
         }
     } else if (warp == W_MMA) {
         // ------------------------------------------------------------ MMA issuer (whole warp walks the loop, lane 0 issues)
-        // The issue loop IS the pace of this kernel when it is long: ncu (profiles/r02_full_gemm_tc_noepi) showed ~75 dependent
-        // SASS instructions per stage (R2UR moves, address arithmetic, one ELECT waterfall per tcgen05 instruction) = ~500 clk
-        // against the 256-clk tensor time of a stage, with every other role waiting on this warp.  So the ring position is a
+        // The issue loop IS the pace of this kernel when it is long: with the epilogue removed the kernel still took ~500 clk per stage
+        // (instruction counters of that capture: ~75 dependent instructions per stage from address arithmetic and the election around
+        // each tcgen05 instruction) against the 256-clk tensor time of a stage, with every other role waiting on this warp.  So the ring position is a
         // compile-time constant here (the loop walks items in groups of TC_STAGES): operand descriptors and barrier addresses
         // are base + immediate, and the only per-stage arithmetic left is the tile bookkeeping.
         constexpr uint32_t idesc = tc_idesc(TC_BM, TC_BN);
