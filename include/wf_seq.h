@@ -15,6 +15,18 @@ extern "C" {
 
 #define WF_SEQ_LATENT_ATTENTION 0  /* sliding-window attention over a cached low-rank latent + one shared rotated key part */
 #define WF_SEQ_DELTA 1             /* gated delta rule with short convolutions */
+#define WF_SEQ_GQA_ATTENTION 2     /* grouped-query softmax attention over cached per-head keys and values (no rotation) */
+
+/* how a layer wraps its sublayers */
+#define WF_SEQ_BLOCK_SANDWICH 0    /* x += norm_b(sub(conv(norm_a(x)))): grouped norms before and after, input convolution with carried tail */
+#define WF_SEQ_BLOCK_POST 1        /* x += residual_mult * gain * rms(sub(x)): the sublayer reads the stream, ONE gain per norm */
+
+/* feed-forward kinds (wf_seq_layer.has_ff) and gated activations (ff_act) */
+#define WF_SEQ_FF_NONE 0
+#define WF_SEQ_FF_ROUTED 1
+#define WF_SEQ_FF_DENSE 2
+#define WF_SEQ_ACT_SILU 0          /* silu(g) * u */
+#define WF_SEQ_ACT_CLAMPED 1       /* g = min(g, limit), u = clamp(u, -limit, limit); g * sigmoid(1.702 g) * (u + 1) */
 
 typedef struct wf_seq_layer {
     int type;
@@ -24,8 +36,23 @@ typedef struct wf_seq_layer {
     float scale, rope_base;
     /* delta */
     int kv_heads, conv;
-    /* routed feed-forward (has_ff = 0: the layer has none) */
+    /* feed-forward: has_ff = WF_SEQ_FF_*; dense uses ff, ff_act, ff_limit only */
     int has_ff, experts, identity, top, groups, keep, ff;
+    /* grouped-query attention: kv_heads key/value heads shared by heads / kv_heads query heads each.  qk_norm / v_norm: queries and keys /
+     * values divided by their root mean square per head; proj_bias: q, k, v and the output projection have biases; head_gate: head h's
+     * output times sigmoid(W_g x)_h; dist_exp > 0: score -= 2^(-dist_exp (h + 1) / heads) * (i - j); kv_from >= 0: no key / value
+     * projections, the layer reads that earlier layer's cache.  window as above (keys i - window < j <= i). */
+    int qk_norm, v_norm, proj_bias, head_gate, kv_from;
+    float dist_exp;
+    /* feed-forward details */
+    int ff_act;                    /* WF_SEQ_ACT_* of the experts (and of a dense feed-forward) */
+    float ff_limit;
+    int router_act;                /* 0 softmax over the experts, 1 sigmoid of each */
+    int group_top;                 /* a group's score = sum of its group_top largest choice scores (<= 1: the largest) */
+    int router_norm;               /* 1: the chosen scores are divided by their sum (+ 1e-20) */
+    float router_scale;            /* the weights are multiplied by this */
+    int shared_ff;                 /* > 0: a shared expert of this size runs for every token, times sigmoid(w_sg x) */
+    float shared_limit;
 } wf_seq_layer;
 
 typedef struct wf_seq_config {
@@ -36,6 +63,10 @@ typedef struct wf_seq_config {
     int page_size, max_pages;      /* cache pool: max_pages pages of page_size tokens (all cached layers of a token share a page) */
     int slots;                     /* sequences alive at once (each owns one state slot and one block-table row) */
     int max_step_tokens;           /* most tokens in one step */
+    int block_form;                /* WF_SEQ_BLOCK_* */
+    float residual_mult;           /* WF_SEQ_BLOCK_POST */
+    int pos_embed;                 /* 1: a sinusoidal position vector is added to the embedding (entry 2i sin, 2i + 1 cos of p * pos_base^(-2i / width)) */
+    float pos_base;
 } wf_seq_config;
 
 typedef struct wf_seq_engine wf_seq_engine;
@@ -75,7 +106,8 @@ int wf_seq_launches_last_step(const wf_seq_engine* e);
  * (float [n_layers, n, width], n = tokens of the step).  wf_seq_run_part runs ONE part of one layer on given float rows (host memory,
  * [n, width]) through the same kernels, caches and state as wf_seq_step, and returns that part's float output [n, width]:
  * 0 first norm, 1 input convolution of the mixer (carried state), 2 the mixer, 3 the feed-forward, 4 input convolution of the
- * feed-forward.  Sequence lengths advance as in a step. */
+ * feed-forward (1 and 4: WF_SEQ_BLOCK_SANDWICH only; part 0 of WF_SEQ_BLOCK_POST is residual_mult * gain * rms(rows)).
+ * Sequence lengths advance as in a step. */
 int wf_seq_set_layer_tap(wf_seq_engine* e, float* host);
 int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, const int32_t* slots, const int32_t* counts, const float* in_host,
                     float* out_host);

@@ -39,6 +39,14 @@ struct LayerState {
     int C = 0;                // convolved channels
     // routed feed-forward
     void *router = nullptr, *correction = nullptr, *wgu = nullptr, *wd = nullptr;
+    int nz = 0;               // rows of the router matrix: the experts, plus the shared expert's gate row when there is one
+    // grouped-query attention: biases, column offsets of the parts inside the fused projection (-1: absent)
+    void *qb = nullptr, *kb = nullptr, *vb = nullptr, *ob = nullptr;
+    int k_off = -1, v_off = -1, g_off = -1;
+    // one gated unit that every token runs: a dense feed-forward, or the shared expert of a routed one.  [gate | up] stacked, then down
+    void *ugu = nullptr, *ud = nullptr;
+    int uff = 0;
+    float ulimit = 0.f;
     // state slot offsets (floats)
     size_t st_canon1 = 0, st_canon2 = 0, st_conv = 0, st_S = 0;
 };
@@ -70,6 +78,8 @@ struct wf_seq_engine {
     float *x = nullptr, *hn = nullptr, *y = nullptr, *proj = nullptr, *qr = nullptr, *qa = nullptr, *ov = nullptr, *qkvc = nullptr, *beta = nullptr,
           *decay = nullptr, *od = nullptr, *z = nullptr, *wts = nullptr, *gu = nullptr, *yexp = nullptr;
     void *hperm = nullptr, *h_t = nullptr, *qn = nullptr, *olat = nullptr, *og = nullptr, *hmid = nullptr, *xn = nullptr;
+    float *gate = nullptr, *ugu = nullptr, *uy = nullptr;      // head gates; the every-token unit's [gate | up] rows and its output
+    void* uhmid = nullptr;
     int32_t *ids = nullptr, *counts = nullptr, *plan_scratch = nullptr, *sorted_rows = nullptr, *pair_row = nullptr, *tile_group = nullptr;
     int P = 0;                        // padded expert-row bound
     int fuse_input = 1;               // norm + input convolution (+ state roll of single-token sequences) in one kernel (WF_SEQ_FUSE_INPUT=0: three kernels)
@@ -128,6 +138,7 @@ int validate(const wf_seq_config& c, const wf_seq_layer* L) {
         set_error("wf_seq_create: vocab %d width %d layers %d norm groups %d taps %d", c.vocab, c.width, c.n_layers, c.norm_groups, c.canon_taps);
         return WF_ERR_INVALID;
     }
+    if (c.block_form != WF_SEQ_BLOCK_SANDWICH && c.block_form != WF_SEQ_BLOCK_POST) { set_error("wf_seq_create: block form %d", c.block_form); return WF_ERR_INVALID; }
     if (c.page_size <= 0 || c.max_pages <= 0 || c.slots <= 0 || c.max_step_tokens <= 0) { set_error("wf_seq_create: page / slot / step sizes must be positive"); return WF_ERR_INVALID; }
     for (int i = 0; i < c.n_layers; ++i) {
         const wf_seq_layer& l = L[i];
@@ -136,8 +147,20 @@ int validate(const wf_seq_config& c, const wf_seq_layer* L) {
             if (l.kv_rank <= 0 || l.rot_dim < 0 || l.window < 1 || l.rope_dims < 0 || l.rope_dims > l.rot_dim || (l.rope_dims & 1)) { set_error("layer %d: latent attention sizes", i); return WF_ERR_INVALID; }
         } else if (l.type == WF_SEQ_DELTA) {
             if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.conv < 1) { set_error("layer %d: delta sizes", i); return WF_ERR_INVALID; }
+        } else if (l.type == WF_SEQ_GQA_ATTENTION) {
+            if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.window < 1) { set_error("layer %d: attention sizes", i); return WF_ERR_INVALID; }
+            if (l.kv_from >= 0) {
+                const wf_seq_layer* src = l.kv_from < i ? &L[l.kv_from] : nullptr;
+                if (!src || src->type != WF_SEQ_GQA_ATTENTION || src->kv_from >= 0 || src->kv_heads != l.kv_heads || src->dim != l.dim || src->vdim != l.vdim) {
+                    set_error("layer %d: kv_from %d must name an earlier attention layer with its own key / value projections and the same key / value sizes", i, l.kv_from);
+                    return WF_ERR_INVALID;
+                }
+            }
         } else { set_error("layer %d: unknown mixer type %d", i, l.type); return WF_ERR_INVALID; }
-        if (l.has_ff) {
+        if (l.has_ff != WF_SEQ_FF_NONE && l.has_ff != WF_SEQ_FF_ROUTED && l.has_ff != WF_SEQ_FF_DENSE) { set_error("layer %d: feed-forward kind %d", i, l.has_ff); return WF_ERR_INVALID; }
+        if (l.has_ff == WF_SEQ_FF_DENSE && l.ff <= 0) { set_error("layer %d: dense feed-forward size", i); return WF_ERR_INVALID; }
+        if (l.has_ff && (l.ff_act < 0 || l.ff_act > 1 || l.shared_ff < 0)) { set_error("layer %d: feed-forward activation / shared size", i); return WF_ERR_INVALID; }
+        if (l.has_ff == WF_SEQ_FF_ROUTED) {
             const int N = l.experts + l.identity;
             if (l.experts < 0 || l.identity < 0 || N <= 0 || l.top < 1 || l.top > N || l.groups < 1 || N % l.groups || l.keep < 1 || l.keep > l.groups || (l.experts > 0 && l.ff <= 0)) {
                 set_error("layer %d: router sizes", i); return WF_ERR_INVALID;
@@ -301,18 +324,61 @@ int run_delta(wf_seq_engine* e, LayerState& L, const Batch& b) {
     return rc;
 }
 
+// h_t -> y float [n, W] (the output projection's bias is NOT added here: the caller's norm kernel takes it)
+int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b) {
+    const wf_seq_layer& c = L.c;
+    const int W = e->cfg.width, n = b.n, nv = c.heads * c.vdim;
+    cudaStream_t s = e->stream;
+    int rc;
+    GqaDims D{c.heads, c.kv_heads, c.dim, c.vdim, c.scale, c.dist_exp, c.window, c.qk_norm, c.v_norm};
+    const LayerState& src = c.kv_from >= 0 ? e->layers[c.kv_from] : L;        // whose cache rows this layer reads
+    PagedCache pc{e->pool, e->page_stride, src.cache_off, e->cfg.page_size, e->d_block_table, e->pt.max_blocks};
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q | k | v | g]
+    mark(e, "attn.proj_gemm");
+    if ((rc = launch_gqa_prep(e->dt, b, D, e->proj, L.np, L.k_off, L.v_off, L.g_off, L.qb, L.kb, L.vb, e->cfg.eps, pc, e->qn, c.head_gate ? e->gate : nullptr, s))) return rc;
+    mark(e, "attn.prep+kv_write");
+    if ((rc = launch_gqa_attn(e->dt, b, D, e->qn, c.head_gate ? e->gate : nullptr, pc, e->og, s))) return rc;
+    mark(e, "attn.attention");
+    rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
+    mark(e, "attn.out_gemm");
+    return rc;
+}
+
 int run_mixer(wf_seq_engine* e, LayerState& L, const Batch& b) {
+    if (L.c.type == WF_SEQ_GQA_ATTENTION) return run_gqa(e, L, b);
     return L.c.type == WF_SEQ_LATENT_ATTENTION ? run_latent(e, L, b) : run_delta(e, L, b);
+}
+
+// the gated unit every token runs (dense feed-forward / shared expert): h_t -> out float [n, W]
+int run_unit(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
+    const int W = e->cfg.width, n = b.n, ff = L.uff;
+    cudaStream_t s = e->stream;
+    int rc;
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.ugu, W, e->ugu, 1, 2 * ff, n, 2 * ff, W), s))) return rc;
+    mark(e, "unit.gate_up");
+    if ((rc = launch_silu_mul(e->dt, e->ugu, n, ff, nullptr, e->uhmid, s, L.c.ff_act, L.ulimit))) return rc;
+    mark(e, "unit.act");
+    rc = launch_gemm(e->dt, lin(e->uhmid, 0, ff, L.ud, ff, out, 1, W, n, W, ff), s);
+    mark(e, "unit.down");
+    return rc;
 }
 
 int run_ff(wf_seq_engine* e, LayerState& L, const Batch& b) {
     const wf_seq_layer& c = L.c;
-    const int W = e->cfg.width, n = b.n, N = c.experts + c.identity;
+    const int W = e->cfg.width, n = b.n, N = L.nz;
     cudaStream_t s = e->stream;
     int rc;
+    if (c.has_ff == WF_SEQ_FF_DENSE) return run_unit(e, L, b, e->y);
     RouterDims R{c.experts, c.identity, c.top, c.groups, c.keep};
-    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.router, W, e->z, 1, N, n, N, W), s))) return rc;
+    R.act = c.router_act; R.group_top = c.group_top; R.norm = c.router_norm; R.scale = c.router_scale;
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.router, W, e->z, 1, N, n, N, W), s))) return rc;     // expert logits [| shared gate logit]
     mark(e, "moe.router");
+    const float* sh_y = nullptr;
+    const float* sh_gate = nullptr;
+    if (c.shared_ff > 0) {
+        if ((rc = run_unit(e, L, b, e->uy))) return rc;
+        sh_y = e->uy; sh_gate = e->z + c.experts + c.identity;
+    }
     const int pairs = n * c.top;
     GemmArgs gp = lin(e->h_t, 0, W, L.wgu, W, e->gu, 1, 2 * c.ff, pairs, 2 * c.ff, W);
     gp.group_stride = (long long)2 * c.ff * W;
@@ -327,11 +393,11 @@ int run_ff(wf_seq_engine* e, LayerState& L, const Batch& b) {
         // few tokens (decoding): one weight-streaming product per (token, expert) pair, no sorting
         if ((rc = launch_gemv_pairs(e->dt, gp, e->ids, c.experts, pairs, c.top, s))) return rc;
         mark(e, "moe.gate_up");
-        if ((rc = launch_silu_mul(e->dt, e->gu, pairs, c.ff, nullptr, e->hmid, s))) return rc;
+        if ((rc = launch_silu_mul(e->dt, e->gu, pairs, c.ff, nullptr, e->hmid, s, c.ff_act, c.ff_limit))) return rc;
         mark(e, "moe.silu_mul");
         if ((rc = launch_gemv_pairs(e->dt, gd, e->ids, c.experts, pairs, 1, s))) return rc;
         mark(e, "moe.down");
-        rc = launch_moe_combine(e->dt, R, n, W, e->ids, e->wts, nullptr, e->yexp, e->h_t, e->y, s);
+        rc = launch_moe_combine(e->dt, R, n, W, e->ids, e->wts, nullptr, e->yexp, e->h_t, e->y, s, sh_y, sh_gate, N);
         mark(e, "moe.combine");
         return rc;
     }
@@ -345,14 +411,14 @@ int run_ff(wf_seq_engine* e, LayerState& L, const Batch& b) {
         g.tile_group = e->tile_group; g.group_stride = (long long)2 * c.ff * W; g.n_groups = c.experts;
         if ((rc = launch_gemm(e->dt, g, s))) return rc;
         mark(e, "moe.gate_up");
-        if ((rc = launch_silu_mul(e->dt, e->gu, P, c.ff, e->tile_group, e->hmid, s))) return rc;
+        if ((rc = launch_silu_mul(e->dt, e->gu, P, c.ff, e->tile_group, e->hmid, s, c.ff_act, c.ff_limit))) return rc;
         mark(e, "moe.silu_mul");
         GemmArgs g2 = lin(e->hmid, 0, c.ff, L.wd, c.ff, e->yexp, 1, W, P, W, c.ff);
         g2.tile_group = e->tile_group; g2.group_stride = (long long)W * c.ff; g2.n_groups = c.experts;
         if ((rc = launch_gemm(e->dt, g2, s))) return rc;
         mark(e, "moe.down");
     }
-    rc = launch_moe_combine(e->dt, R, n, W, e->ids, e->wts, e->pair_row, e->yexp, e->h_t, e->y, s);
+    rc = launch_moe_combine(e->dt, R, n, W, e->ids, e->wts, e->pair_row, e->yexp, e->h_t, e->y, s, sh_y, sh_gate, N);
     mark(e, "moe.combine");
     return rc;
 }
@@ -380,7 +446,38 @@ int run_input(wf_seq_engine* e, const Batch& b, const void* norm_w, const void* 
     return rc;
 }
 
+// WF_SEQ_BLOCK_POST: every sublayer reads the stream itself (h_t is its storage-type copy, refreshed by the kernel that updates the stream)
+// and its output is normalised with one gain, scaled and added.
+int run_layers_post(wf_seq_engine* e, const StepView& v) {
+    const int W = e->cfg.width, n = v.b.n;
+    const float mult = e->cfg.residual_mult, eps = e->cfg.eps;
+    cudaStream_t s = e->stream;
+    int rc;
+    if (e->cfg.pos_embed) { if ((rc = launch_embed_pos(e->dt, e->embed, v.tokens, v.b.tok_pos, n, W, e->cfg.pos_base, e->x, e->h_t, s))) return rc; }
+    else {
+        if ((rc = launch_embed_f32(e->dt, e->embed, v.tokens, n, W, e->x, s))) return rc;
+        if ((rc = launch_round_rows(e->dt, e->x, n, W, e->h_t, s))) return rc;
+    }
+    mark(e, "embed");
+    for (int li = 0; li < e->cfg.n_layers; ++li) {
+        LayerState& L = e->layers[li];
+        if ((rc = run_mixer(e, L, v.b))) return rc;
+        if ((rc = launch_scalar_rmsnorm(e->dt, e->y, W, L.ob, L.norm1, mult, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s))) return rc;
+        mark(e, "norm+residual");
+        if (L.c.has_ff) {
+            if ((rc = run_ff(e, L, v.b))) return rc;
+            if ((rc = launch_scalar_rmsnorm(e->dt, e->y, W, nullptr, L.norm2, mult, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s))) return rc;
+            mark(e, "norm+residual");
+        }
+        if (e->layer_tap) {
+            if (cuda_check(cudaMemcpyAsync(e->layer_tap + (size_t)li * n * W, e->x, (size_t)n * W * 4, cudaMemcpyDeviceToHost, s), "layer tap")) return WF_ERR_CUDA;
+        }
+    }
+    return WF_OK;
+}
+
 int run_layers(wf_seq_engine* e, const StepView& v) {
+    if (e->cfg.block_form == WF_SEQ_BLOCK_POST) return run_layers_post(e, v);
     const int W = e->cfg.width, n = v.b.n;
     cudaStream_t s = e->stream;
     int rc;
@@ -422,7 +519,9 @@ int run_head(wf_seq_engine* e, const StepView& v, int nwant) {
     const int W = e->cfg.width;
     int rc;
     if ((rc = ensure_logits(e, nwant))) return rc;
-    if ((rc = launch_group_rmsnorm(e->dt, e->x, W, e->final_norm, e->cfg.norm_groups, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream))) return rc;
+    if (e->cfg.block_form == WF_SEQ_BLOCK_POST) rc = launch_scalar_rmsnorm(e->dt, e->x, W, nullptr, e->final_norm, 1.f, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream);
+    else rc = launch_group_rmsnorm(e->dt, e->x, W, e->final_norm, e->cfg.norm_groups, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream);
+    if (rc) return rc;
     rc = launch_gemm(e->dt, lin(e->xn, 0, W, e->head, W, e->logits, 1, e->cfg.vocab, nwant, e->cfg.vocab, W), e->stream);
     mark(e, "final_norm+head_gemm");
     return rc;
@@ -489,13 +588,15 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
 #define TRY(x) do { if ((rc = (x))) { wf_seq_destroy(e); return rc; } } while (0)
     if (cuda_check(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking), "stream")) { delete e; return WF_ERR_CUDA; }
     TRY(dalloc_t(e, &e->embed, (size_t)c.vocab * W));
-    TRY(dalloc_t(e, &e->final_norm, W));
+    const bool post = c.block_form == WF_SEQ_BLOCK_POST;
+    const size_t norm_elems = post ? 1 : W;              // the post form's norms have a single gain
+    TRY(dalloc_t(e, &e->final_norm, norm_elems));
     TRY(dalloc_t(e, &e->head, (size_t)c.vocab * W));
     add_tensor(e, "embed", e->embed, (size_t)c.vocab * W);
-    add_tensor(e, "final.norm", e->final_norm, W);
+    add_tensor(e, "final.norm", e->final_norm, norm_elems);
     add_tensor(e, "head", e->head, (size_t)c.vocab * W);
     // maxima over layers for the shared workspaces
-    size_t max_np = 1, max_hd = 1, max_hr = 1, max_hrot = 1, max_hv = 1, max_C = 1, max_H = 1, max_N = 1, max_top = 1, max_E = 1, max_ff = 1;
+    size_t max_np = 1, max_hd = 1, max_hr = 1, max_hrot = 1, max_hv = 1, max_C = 1, max_H = 1, max_N = 1, max_top = 1, max_E = 1, max_ff = 1, max_uff = 0;
     long long cache_elems = 0;
     size_t st = 0;
     e->layers.resize(c.n_layers);
@@ -504,18 +605,53 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
         L.c = layers[li];
         const wf_seq_layer& l = L.c;
         const std::string p = "l" + std::to_string(li) + ".";
-        void** norms[4] = {&L.norm1, &L.norm1b, &L.norm2, &L.norm2b};
-        const char* norm_names[4] = {"norm1", "norm1b", "norm2", "norm2b"};
-        for (int k = 0; k < (l.has_ff ? 4 : 2); ++k) { TRY(dalloc_t(e, norms[k], W)); add_tensor(e, p + norm_names[k], *norms[k], W); }
-        TRY(dalloc_t(e, &L.canon1, (size_t)W * taps)); add_tensor(e, p + "canon1", L.canon1, (size_t)W * taps);
-        L.st_canon1 = st; st += (size_t)(taps - 1) * W;
-        if (l.has_ff) {
-            TRY(dalloc_t(e, &L.canon2, (size_t)W * taps)); add_tensor(e, p + "canon2", L.canon2, (size_t)W * taps);
-            L.st_canon2 = st; st += (size_t)(taps - 1) * W;
+        L.norm1 = L.norm2 = L.norm1b = L.norm2b = L.canon1 = L.canon2 = nullptr;
+        if (post) {
+            TRY(dalloc_t(e, &L.norm1, 1)); add_tensor(e, p + "norm1", L.norm1, 1);
+            if (l.has_ff) { TRY(dalloc_t(e, &L.norm2, 1)); add_tensor(e, p + "norm2", L.norm2, 1); }
+        } else {
+            void** norms[4] = {&L.norm1, &L.norm1b, &L.norm2, &L.norm2b};
+            const char* norm_names[4] = {"norm1", "norm1b", "norm2", "norm2b"};
+            for (int k = 0; k < (l.has_ff ? 4 : 2); ++k) { TRY(dalloc_t(e, norms[k], W)); add_tensor(e, p + norm_names[k], *norms[k], W); }
+            TRY(dalloc_t(e, &L.canon1, (size_t)W * taps)); add_tensor(e, p + "canon1", L.canon1, (size_t)W * taps);
+            L.st_canon1 = st; st += (size_t)(taps - 1) * W;
+            if (l.has_ff) {
+                TRY(dalloc_t(e, &L.canon2, (size_t)W * taps)); add_tensor(e, p + "canon2", L.canon2, (size_t)W * taps);
+                L.st_canon2 = st; st += (size_t)(taps - 1) * W;
+            }
         }
         const size_t nv = (size_t)l.heads * l.vdim;
         TRY(dalloc_t(e, &L.wo, (size_t)W * nv)); add_tensor(e, p + "mix.o", L.wo, (size_t)W * nv);
-        if (l.type == WF_SEQ_LATENT_ATTENTION) {
+        if (l.type == WF_SEQ_GQA_ATTENTION) {
+            const size_t nq = (size_t)l.heads * l.dim, nk = (size_t)l.kv_heads * l.dim, nvk = (size_t)l.kv_heads * l.vdim;
+            const bool own = l.kv_from < 0;
+            size_t off = nq;
+            if (own) { L.k_off = (int)off; off += nk; L.v_off = (int)off; off += nvk; }
+            if (l.head_gate) { L.g_off = (int)off; off += l.heads; }
+            L.np = (int)off;
+            TRY(dalloc_t(e, &L.wp, (size_t)L.np * W));
+            add_tensor(e, p + "mix.q", L.wp, nq * W);
+            if (own) {
+                add_tensor(e, p + "mix.k", at(e, L.wp, (size_t)L.k_off * W), nk * W);
+                add_tensor(e, p + "mix.v", at(e, L.wp, (size_t)L.v_off * W), nvk * W);
+            }
+            if (l.head_gate) add_tensor(e, p + "mix.g", at(e, L.wp, (size_t)L.g_off * W), (size_t)l.heads * W);
+            if (l.proj_bias) {
+                TRY(dalloc_t(e, &L.qb, nq)); add_tensor(e, p + "mix.q.b", L.qb, nq);
+                if (own) {
+                    TRY(dalloc_t(e, &L.kb, nk)); add_tensor(e, p + "mix.k.b", L.kb, nk);
+                    TRY(dalloc_t(e, &L.vb, nvk)); add_tensor(e, p + "mix.v.b", L.vb, nvk);
+                }
+                TRY(dalloc_t(e, &L.ob, W)); add_tensor(e, p + "mix.o.b", L.ob, W);
+            }
+            if (own) {
+                // every layer's part of a page starts 16-byte aligned
+                cache_elems = (cache_elems + 7) / 8 * 8;
+                L.cache_off = cache_elems;
+                cache_elems += (long long)c.page_size * (nk + nvk);
+            }
+            max_hd = std::max(max_hd, nq);
+        } else if (l.type == WF_SEQ_LATENT_ATTENTION) {
             const size_t nq = (size_t)l.heads * (l.dim + l.rot_dim), nkv = l.kv_rank + l.rot_dim;
             L.np = (int)(nq + nkv + nv);
             TRY(dalloc_t(e, &L.wp, (size_t)L.np * W));
@@ -553,9 +689,26 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
             max_C = std::max(max_C, (size_t)L.C);
         }
         max_np = std::max(max_np, (size_t)L.np); max_hv = std::max(max_hv, nv); max_H = std::max(max_H, (size_t)l.heads);
-        if (l.has_ff) {
+        if (l.has_ff == WF_SEQ_FF_DENSE) {
+            L.uff = l.ff; L.ulimit = l.ff_limit;
+            TRY(dalloc_t(e, &L.ugu, (size_t)2 * l.ff * W)); TRY(dalloc_t(e, &L.ud, (size_t)W * l.ff));
+            add_tensor(e, p + "mlp.gate", L.ugu, (size_t)l.ff * W);
+            add_tensor(e, p + "mlp.up", at(e, L.ugu, (size_t)l.ff * W), (size_t)l.ff * W);
+            add_tensor(e, p + "mlp.down", L.ud, (size_t)W * l.ff);
+            max_uff = std::max(max_uff, (size_t)l.ff);
+        } else if (l.has_ff == WF_SEQ_FF_ROUTED) {
             const size_t N = l.experts + l.identity;
-            TRY(dalloc_t(e, &L.router, N * W)); add_tensor(e, p + "mlp.router", L.router, N * W);
+            L.nz = (int)N + (l.shared_ff > 0 ? 1 : 0);
+            TRY(dalloc_t(e, &L.router, (size_t)L.nz * W)); add_tensor(e, p + "mlp.router", L.router, N * W);
+            if (l.shared_ff > 0) {
+                L.uff = l.shared_ff; L.ulimit = l.shared_limit;
+                add_tensor(e, p + "mlp.shared.sg", at(e, L.router, N * W), W);
+                TRY(dalloc_t(e, &L.ugu, (size_t)2 * l.shared_ff * W)); TRY(dalloc_t(e, &L.ud, (size_t)W * l.shared_ff));
+                add_tensor(e, p + "mlp.shared.gate", L.ugu, (size_t)l.shared_ff * W);
+                add_tensor(e, p + "mlp.shared.up", at(e, L.ugu, (size_t)l.shared_ff * W), (size_t)l.shared_ff * W);
+                add_tensor(e, p + "mlp.shared.down", L.ud, (size_t)W * l.shared_ff);
+                max_uff = std::max(max_uff, (size_t)l.shared_ff);
+            }
             TRY(dalloc_t(e, &L.correction, N)); add_tensor(e, p + "mlp.correction", L.correction, N);
             if (l.experts > 0) {
                 TRY(dalloc_t(e, &L.wgu, (size_t)l.experts * 2 * l.ff * W));
@@ -567,7 +720,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
                     add_tensor(e, ep + "down", at(e, L.wd, (size_t)x * W * l.ff), (size_t)W * l.ff);
                 }
             }
-            max_N = std::max(max_N, N); max_top = std::max(max_top, (size_t)l.top); max_E = std::max(max_E, (size_t)std::max(l.experts, 1));
+            max_N = std::max(max_N, (size_t)L.nz); max_top = std::max(max_top, (size_t)l.top); max_E = std::max(max_E, (size_t)std::max(l.experts, 1));
             max_ff = std::max(max_ff, (size_t)std::max(l.ff, 1));
             const int P = (T * l.top + GEMM_BM - 1) / GEMM_BM * GEMM_BM + l.experts * GEMM_BM;
             e->P = std::max(e->P, P);
@@ -594,6 +747,8 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     TRY(dalloc_t(e, &e->olat, (size_t)T * max_hr)); TRY(dalloc_n(e, &e->ov, (size_t)T * max_hv)); TRY(dalloc_t(e, &e->og, (size_t)T * max_hv));
     e->attn_ws_rows = 4 * 148;
     if (e->dt == WF_BF16 && max_hr > 1) TRY(dalloc_bytes(e, (void**)&e->attn_ws, (size_t)e->attn_ws_rows * (max_hr + 2 * max_H) * sizeof(float)));
+    TRY(dalloc_n(e, &e->gate, (size_t)T * max_H));
+    if (max_uff) { TRY(dalloc_n(e, &e->ugu, (size_t)T * 2 * max_uff)); TRY(dalloc_t(e, &e->uhmid, (size_t)T * max_uff)); TRY(dalloc_n(e, &e->uy, (size_t)T * W)); }
     TRY(dalloc_n(e, &e->qkvc, (size_t)T * max_C)); TRY(dalloc_n(e, &e->beta, (size_t)T * max_H)); TRY(dalloc_n(e, &e->decay, (size_t)T * max_H));
     TRY(dalloc_n(e, &e->od, (size_t)T * max_hv));
     TRY(dalloc_n(e, &e->z, (size_t)T * max_N)); TRY(dalloc_n(e, &e->ids, (size_t)T * max_top)); TRY(dalloc_n(e, &e->wts, (size_t)T * max_top));
@@ -729,7 +884,13 @@ extern "C" int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, 
     cudaStream_t s = e->stream;
     const size_t bytes = (size_t)n * W * 4;
     float* result = e->y;
-    if (part == 0) {
+    const bool post = e->cfg.block_form == WF_SEQ_BLOCK_POST;
+    if (post && (part == 1 || part == 4)) { set_error("wf_seq_run_part: this model's sublayers have no input convolution"); return WF_ERR_INVALID; }
+    if (part == 0 && post) {
+        if (cuda_check(cudaMemcpyAsync(e->x, in_host, bytes, cudaMemcpyHostToDevice, s), "in")) return WF_ERR_CUDA;
+        rc = launch_scalar_rmsnorm(e->dt, e->x, W, nullptr, L.norm1, e->cfg.residual_mult, e->cfg.eps, n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s);
+        result = e->hn;
+    } else if (part == 0) {
         if (cuda_check(cudaMemcpyAsync(e->x, in_host, bytes, cudaMemcpyHostToDevice, s), "in")) return WF_ERR_CUDA;
         rc = launch_group_rmsnorm(e->dt, e->x, W, L.norm1, e->cfg.norm_groups, e->cfg.eps, n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s);
         result = e->hn;
@@ -745,6 +906,7 @@ extern "C" int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, 
         // round the given rows to the storage type exactly as the input convolution's output would be
         rc = launch_gate_mul(e->dt, e->hn, W, e->hn, W, 2, n, W, e->h_t, W, s);
         if (!rc) rc = part == 2 ? run_mixer(e, L, v.b) : run_ff(e, L, v.b);
+        if (!rc && part == 2 && L.ob) rc = launch_add_bias(e->dt, e->y, W, L.ob, n, W, s);
     } else { set_error("wf_seq_run_part: unknown part %d", part); return WF_ERR_INVALID; }
     if (rc) return rc;
     if (cuda_check(cudaMemcpyAsync(out_host, result, bytes, cudaMemcpyDeviceToHost, s), "out")) return WF_ERR_CUDA;

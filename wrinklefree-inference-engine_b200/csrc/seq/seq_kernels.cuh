@@ -15,6 +15,15 @@ int launch_embed_f32(int dt, const void* table, const int32_t* tokens, int n, in
 // strides ldx / ldy (res shares ldy; y may alias res); rows: optional gather of the input AND residual rows.  y_t: optional T copy of y.
 int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int groups, float eps, int n, int W, const float* res, float* y,
                          int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s);
+// x[i, :] = table[tokens[i], :] + sinusoidal position vector of tok_pos[i] (entry 2k sin, 2k + 1 cos of pos * base^(-2k / W)); x_t: optional T copy
+int launch_embed_pos(int dt, const void* table, const int32_t* tokens, const int32_t* tok_pos, int n, int W, float base, float* x, void* x_t, cudaStream_t s);
+// x_t T [n, W] = x float [n, W] rounded to the storage type (dense rows)
+int launch_round_rows(int dt, const float* x, int n, int W, void* x_t, cudaStream_t s);
+// RMS norm with a single gain (gain: one T element): out = [res +] mult * gain * (y + bias) / sqrt(mean((y + bias)^2) + eps).  bias T [W] or null;
+// out float (may alias res) and / or out_t T; rows: optional gather of the input AND residual rows.
+int launch_scalar_rmsnorm(int dt, const float* y, int ldy, const void* bias, const void* gain, float mult, float eps, int n, int W, const float* res, float* out,
+                          int ldo, void* out_t, int ldt, const int32_t* rows, cudaStream_t s);
+int launch_add_bias(int dt, float* y, int ld, const void* bias, int n, int W, cudaStream_t s);
 // causal depthwise taps over time with carried state: out_t = [identity ? in_t : 0] + sum_j w[c, j] * in_(t - taps + 1 + j), optional silu.
 // in float [n, C] (ld_in); state float [slot][taps - 1][C] (slot_stride floats between slots) = the last taps - 1 inputs of each sequence,
 // read here and rolled forward by launch_taps_state AFTER this kernel.  out: T [n, C] (out_t) and / or float (out_f).
@@ -92,6 +101,20 @@ int launch_gate_mul(int dt, const float* x, int ldx, const float* g, int ldg, in
 // out T [H][C][R] = in T [H][R][C]   (per-head transpose, done once at load)
 int launch_transpose_heads(int dt, const void* in, int H, int R, int C, void* out, cudaStream_t s);
 
+// ---- grouped-query attention (seq_attn.cu) ----------------------------------------------------------------------------------------
+struct GqaDims { int H, G, d, dv; float scale, dist_exp; int window, qk_norm, v_norm; };
+// elements one layer's keys and values take in a cache page: keys [G][page_size][d], then values [G][page_size][dv]
+long long gqa_cache_elems(const GqaDims& D, int page_size);
+// proj float [n, ld]: queries at column 0 (H * d), keys at k_off (G * d), values at v_off (G * dv), gate logits at g_off (H); negative
+// offsets: that part is absent (k_off and v_off together: the layer reads another layer's cache).  Adds the biases (T, or null), divides
+// by the root mean square per head where D says so; queries -> qn T [n, H, d]; keys / values -> the token's cache row; gate float [n, H]
+// = sigmoid of the gate logits (1 when g_off < 0; gate null: not written).
+int launch_gqa_prep(int dt, const Batch& b, const GqaDims& D, const float* proj, int ld, int k_off, int v_off, int g_off, const void* qb, const void* kb,
+                    const void* vb, float eps, const PagedCache& pc, void* qn, float* gate, cudaStream_t s);
+// out T [n, H * dv]: per (token, head) softmax over keys j in (pos - window, pos] of q . k_j * scale - slope_h * (pos - j), weighted value
+// sum, times gate[n, H] (null: no gate).
+int launch_gqa_attn(int dt, const Batch& b, const GqaDims& D, const void* qn, const float* gate, const PagedCache& pc, void* out, cudaStream_t s);
+
 // ---- gated delta rule ----------------------------------------------------------------------------------------------------
 struct DeltaDims { int H, Hk, d, dv; };
 // in place on qkv float [n, C = 2 * Hk * d + H * dv] (ld): q and k heads -> unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times d^-1/2.
@@ -105,7 +128,13 @@ int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int 
 int launch_delta_post(int dt, const DeltaDims& D, int n, const float* o, const void* w, float eps, const float* g, int ldg, void* y, cudaStream_t s);
 
 // ---- routed feed-forward ---------------------------------------------------------------------------------------------------
-struct RouterDims { int E, I, top, groups, keep; };   // E real experts, I identity experts (indices E .. E + I - 1)
+struct RouterDims {
+    int E, I, top, groups, keep;   // E real experts, I identity experts (indices E .. E + I - 1)
+    int act = 0;                   // scores: 0 softmax over all outputs, 1 sigmoid of each
+    int group_top = 1;             // a group's score is the sum of this many of its largest choice scores
+    int norm = 0;                  // 1: weights divided by the sum of the chosen scores (+ 1e-20)
+    float scale = 1.f;             // weights multiplied by this
+};
 // z float [n, E + I] (ldz) -> ids [n, top], wts [n, top]; counts[E] += tokens per real expert (zero on entry; null: not counted)
 int launch_moe_route(int dt, const RouterDims& R, int n, const float* z, int ldz, const void* correction, int32_t* ids, float* wts,
                      int32_t* counts, cudaStream_t s);
@@ -114,11 +143,13 @@ int launch_moe_route(int dt, const RouterDims& R, int n, const float* z, int ldz
 // scratch: 2 * E + 1 ints.
 int launch_moe_plan(const RouterDims& R, int n, const int32_t* ids, const int32_t* counts, int32_t* scratch, int32_t* sorted_rows,
                     int32_t* pair_row, int32_t* tile_group, int P, cudaStream_t s);
-// hmid T [P, ff] = silu(gu[:, :ff]) * gu[:, ff:]   (gu float [P, 2 ff]); rows of skipped tiles are left alone
-int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s);   // tile_group null: every row
+// hmid T [P, ff] = act(gu[:, :ff], gu[:, ff:])   (gu float [P, 2 ff]); rows of skipped tiles are left alone (tile_group null: every row).
+// act 0: silu(g) * u;  act 1: g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(1.702 g) * (u + 1)
+int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s, int act = 0, float limit = 0.f);
 // out float [n, W] = sum_k wts[t, k] * (ids[t, k] < E ? y[pair_row[t, k], :] : h[t, :])     (h T [n, W]; pair_row null: row t * top + k)
+// shared_y (optional, float [n, W]): a shared expert's output, added times sigmoid(shared_gate[i * ld_gate]) (shared_gate null: times 1)
 int launch_moe_combine(int dt, const RouterDims& R, int n, int W, const int32_t* ids, const float* wts, const int32_t* pair_row, const float* y,
-                       const void* h, float* out, cudaStream_t s);
+                       const void* h, float* out, cudaStream_t s, const float* shared_y = nullptr, const float* shared_gate = nullptr, int ld_gate = 0);
 
 // ---- sampling ----------------------------------------------------------------------------------------------------------------
 // next[i] = argmax (temperature <= 0) or a draw from softmax(logits / temperature) restricted to the top_k largest (0 = all) and the

@@ -1,4 +1,5 @@
-// Routed feed-forward: softmax router with an additive choice correction, group-limited top-k choice, identity experts, and the
+// Routed feed-forward: softmax or sigmoid router with an additive choice correction, group-limited top-k choice (groups ranked by their
+// largest choice score or by the sum of their few largest), identity experts, an optional gated shared expert in the combine, and the
 // bookkeeping that turns the chosen (token, expert) pairs into expert-contiguous, tile-padded row ranges for the grouped matrix products.
 #include "seq_kernels.cuh"
 #include <math.h>
@@ -28,20 +29,35 @@ __global__ void moe_route_kernel(RouterDims R, const float* __restrict__ z, int 
     float* gs = ch + N;
     const int i = blockIdx.x, lane = threadIdx.x;
     const float* zr = z + (size_t)i * ldz;
-    float mx = -INFINITY;
-    for (int e = lane; e < N; e += 32) mx = fmaxf(mx, zr[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < N; e += 32) { const float p = expf(zr[e] - mx); sc[e] = p; sum += p; }
-    sum = warp_sum(sum);
-    const float inv = 1.f / sum;
-    for (int e = lane; e < N; e += 32) { sc[e] *= inv; ch[e] = sc[e] + to_f(correction[e]); }
+    if (R.act == 1) {
+        for (int e = lane; e < N; e += 32) { sc[e] = sigmoid_f(zr[e]); ch[e] = sc[e] + to_f(correction[e]); }
+    } else {
+        float mx = -INFINITY;
+        for (int e = lane; e < N; e += 32) mx = fmaxf(mx, zr[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < N; e += 32) { const float p = expf(zr[e] - mx); sc[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        const float inv = 1.f / sum;
+        for (int e = lane; e < N; e += 32) { sc[e] *= inv; ch[e] = sc[e] + to_f(correction[e]); }
+    }
     __syncwarp();
-    // group score = largest choice score of the group; keep the best `keep` groups
+    // group score = sum of the group's group_top largest choice scores (the largest alone when group_top <= 1); keep the best `keep` groups
     for (int g = lane; g < R.groups; g += 32) {
-        float m = -INFINITY;
-        for (int e = g * gsz; e < (g + 1) * gsz; ++e) m = fmaxf(m, ch[e]);
-        gs[g] = m;
+        float acc = 0.f;
+        int prev_e = -1;
+        float prev_v = INFINITY;
+        const int take = R.group_top < 1 ? 1 : (R.group_top < gsz ? R.group_top : gsz);
+        for (int r = 0; r < take; ++r) {       // r-th largest: the largest entry that comes after (prev_v, prev_e) in (value desc, index asc) order
+            float m = -INFINITY; int me = -1;
+            for (int e = g * gsz; e < (g + 1) * gsz; ++e) {
+                const float x = ch[e];
+                const bool after = x < prev_v || (x == prev_v && e > prev_e);
+                if (after && (me < 0 || x > m)) { m = x; me = e; }
+            }
+            acc += m; prev_v = m; prev_e = me;
+        }
+        gs[g] = acc;
     }
     __syncwarp();
     if (R.keep < R.groups) {
@@ -68,6 +84,14 @@ __global__ void moe_route_kernel(RouterDims R, const float* __restrict__ z, int 
             if (counts && ei < R.E) atomicAdd(&counts[ei], 1);
         }
         __syncwarp();
+    }
+    if (R.norm || R.scale != 1.f) {
+        float* w = wts + (size_t)i * R.top;
+        float tot = 0.f;
+        if (R.norm) for (int k = 0; k < R.top; ++k) tot += w[k];       // every lane, same order: identical sums
+        const float mul = R.norm ? R.scale / (tot + 1e-20f) : R.scale;
+        __syncwarp();
+        for (int k = lane; k < R.top; k += 32) w[k] *= mul;
     }
 }
 
@@ -97,7 +121,7 @@ __global__ void moe_plan_kernel(RouterDims R, int n, const int32_t* __restrict__
 
 // VEC = 4: ff a multiple of 4 (16-byte loads of the gate and up halves)
 template <typename T, int VEC>
-__global__ void silu_mul_kernel(const float* __restrict__ gu, int ff, const int32_t* __restrict__ tile_group, T* __restrict__ hmid) {
+__global__ void silu_mul_kernel(const float* __restrict__ gu, int ff, const int32_t* __restrict__ tile_group, T* __restrict__ hmid, int act, float limit) {
     const int r = blockIdx.x;
     if (tile_group && tile_group[r / GEMM_BM] < 0) return;
     const float* row = gu + (size_t)r * 2 * ff;
@@ -109,15 +133,24 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, int ff, const int3
             u[0] = b.x; u[1 % VEC] = b.y; u[2 % VEC] = b.z; u[3 % VEC] = b.w;
         } else { g[0] = row[c]; u[0] = row[ff + c]; }
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) hmid[(size_t)r * ff + c + v] = from_f<T>(silu_f(g[v]) * u[v]);
+        for (int v = 0; v < VEC; ++v) {
+            float a;
+            if (act == 1) {
+                const float gg = fminf(g[v], limit), uu = fminf(fmaxf(u[v], -limit), limit);
+                a = gg * sigmoid_f(1.702f * gg) * (uu + 1.f);
+            } else a = silu_f(g[v]) * u[v];
+            hmid[(size_t)r * ff + c + v] = from_f<T>(a);
+        }
     }
 }
 
 // VEC = 4: W a multiple of 4
 template <typename T, int VEC>
 __global__ void moe_combine_kernel(RouterDims R, int W, const int32_t* __restrict__ ids, const float* __restrict__ wts, const int32_t* __restrict__ pair_row,
-                                   const float* __restrict__ y, const T* __restrict__ h, float* __restrict__ out) {
+                                   const float* __restrict__ y, const T* __restrict__ h, float* __restrict__ out, const float* __restrict__ shared_y,
+                                   const float* __restrict__ shared_gate, int ld_gate) {
     const int i = blockIdx.x;
+    const float sg = shared_y ? (shared_gate ? sigmoid_f(shared_gate[(size_t)i * ld_gate]) : 1.f) : 0.f;
     for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC; c < W; c += gridDim.y * blockDim.x * VEC) {
         float acc[VEC];
 #pragma unroll
@@ -137,6 +170,10 @@ __global__ void moe_combine_kernel(RouterDims R, int W, const int32_t* __restric
             }
 #pragma unroll
             for (int v = 0; v < VEC; ++v) acc[v] = fmaf(w, val[v], acc[v]);
+        }
+        if (shared_y) {
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] = fmaf(sg, shared_y[(size_t)i * W + c + v], acc[v]);
         }
 #pragma unroll
         for (int v = 0; v < VEC; ++v) out[(size_t)i * W + c + v] = acc[v];
@@ -168,24 +205,24 @@ int launch_moe_plan(const RouterDims& R, int n, const int32_t* ids, const int32_
     return launch_check(cudaGetLastError(), "moe_plan");
 }
 
-int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s) {
+int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s, int act, float limit) {
     if (P <= 0) return WF_OK;
     const bool vec = ff % 4 == 0 && (((uintptr_t)gu) & 15) == 0;
     const int per = 128 * (vec ? 4 : 1);
     const dim3 grid(P, P < 256 ? (ff + per - 1) / per : 1);
-    if (dt == WF_BF16) { if (vec) silu_mul_kernel<__nv_bfloat16, 4><<<grid, 128, 0, s>>>(gu, ff, tile_group, (__nv_bfloat16*)hmid); else silu_mul_kernel<__nv_bfloat16, 1><<<grid, 128, 0, s>>>(gu, ff, tile_group, (__nv_bfloat16*)hmid); }
-    else { if (vec) silu_mul_kernel<float, 4><<<grid, 128, 0, s>>>(gu, ff, tile_group, (float*)hmid); else silu_mul_kernel<float, 1><<<grid, 128, 0, s>>>(gu, ff, tile_group, (float*)hmid); }
+    if (dt == WF_BF16) { if (vec) silu_mul_kernel<__nv_bfloat16, 4><<<grid, 128, 0, s>>>(gu, ff, tile_group, (__nv_bfloat16*)hmid, act, limit); else silu_mul_kernel<__nv_bfloat16, 1><<<grid, 128, 0, s>>>(gu, ff, tile_group, (__nv_bfloat16*)hmid, act, limit); }
+    else { if (vec) silu_mul_kernel<float, 4><<<grid, 128, 0, s>>>(gu, ff, tile_group, (float*)hmid, act, limit); else silu_mul_kernel<float, 1><<<grid, 128, 0, s>>>(gu, ff, tile_group, (float*)hmid, act, limit); }
     return launch_check(cudaGetLastError(), "silu_mul");
 }
 
 int launch_moe_combine(int dt, const RouterDims& R, int n, int W, const int32_t* ids, const float* wts, const int32_t* pair_row, const float* y,
-                       const void* h, float* out, cudaStream_t s) {
+                       const void* h, float* out, cudaStream_t s, const float* shared_y, const float* shared_gate, int ld_gate) {
     if (n <= 0) return WF_OK;
     const bool vec = W % 4 == 0 && (((uintptr_t)y) & 15) == 0 && (((uintptr_t)out) & 15) == 0;
     const int per = 256 * (vec ? 4 : 1);
     const dim3 grid(n, n < 64 ? (W + per - 1) / per : 1);       // few tokens: spread a row over several blocks
-    if (dt == WF_BF16) { if (vec) moe_combine_kernel<__nv_bfloat16, 4><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const __nv_bfloat16*)h, out); else moe_combine_kernel<__nv_bfloat16, 1><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const __nv_bfloat16*)h, out); }
-    else { if (vec) moe_combine_kernel<float, 4><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const float*)h, out); else moe_combine_kernel<float, 1><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const float*)h, out); }
+    if (dt == WF_BF16) { if (vec) moe_combine_kernel<__nv_bfloat16, 4><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const __nv_bfloat16*)h, out, shared_y, shared_gate, ld_gate); else moe_combine_kernel<__nv_bfloat16, 1><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const __nv_bfloat16*)h, out, shared_y, shared_gate, ld_gate); }
+    else { if (vec) moe_combine_kernel<float, 4><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const float*)h, out, shared_y, shared_gate, ld_gate); else moe_combine_kernel<float, 1><<<grid, 256, 0, s>>>(R, W, ids, wts, pair_row, y, (const float*)h, out, shared_y, shared_gate, ld_gate); }
     return launch_check(cudaGetLastError(), "moe_combine");
 }
 

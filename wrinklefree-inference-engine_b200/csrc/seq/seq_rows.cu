@@ -18,6 +18,106 @@ int launch_embed_f32(int dt, const void* table, const int32_t* tokens, int n, in
     return launch_check(cudaGetLastError(), "embed_f32");
 }
 
+// x[i, :] = table[tokens[i], :] + position vector of tok_pos[i]: entry 2k = sin(a), entry 2k + 1 = cos(a), a = pos * base^(-2k / W).
+// The frequency and the angle are formed in double so that the float result is the correctly rounded one also at large positions.
+template <typename T>
+__global__ void embed_pos_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens, const int32_t* __restrict__ tok_pos, int W, float base,
+                                 float* __restrict__ x, T* __restrict__ x_t) {
+    const int i = blockIdx.x;
+    const T* row = table + (size_t)tokens[i] * W;
+    const double pos = (double)tok_pos[i], lb = log2((double)base);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const double a = pos * exp2(-2.0 * (double)(c >> 1) / (double)W * lb);
+        const float v = to_f(row[c]) + (float)((c & 1) ? cos(a) : sin(a));
+        x[(size_t)i * W + c] = v;
+        if (x_t) x_t[(size_t)i * W + c] = from_f<T>(v);
+    }
+}
+
+int launch_embed_pos(int dt, const void* table, const int32_t* tokens, const int32_t* tok_pos, int n, int W, float base, float* x, void* x_t, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (dt == WF_BF16) embed_pos_kernel<<<n, 256, 0, s>>>((const __nv_bfloat16*)table, tokens, tok_pos, W, base, x, (__nv_bfloat16*)x_t);
+    else embed_pos_kernel<<<n, 256, 0, s>>>((const float*)table, tokens, tok_pos, W, base, x, (float*)x_t);
+    return launch_check(cudaGetLastError(), "embed_pos");
+}
+
+// x_t[i, :] = T(x[i, :])
+template <typename T>
+__global__ void round_rows_kernel(const float* __restrict__ x, size_t count, T* __restrict__ x_t) {
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < count; k += (size_t)gridDim.x * blockDim.x) x_t[k] = from_f<T>(x[k]);
+}
+
+int launch_round_rows(int dt, const float* x, int n, int W, void* x_t, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    const size_t count = (size_t)n * W;
+    const int blocks = (int)((count + 255) / 256 > 4096 ? 4096 : (count + 255) / 256);
+    if (dt == WF_BF16) round_rows_kernel<<<blocks, 256, 0, s>>>(x, count, (__nv_bfloat16*)x_t);
+    else round_rows_kernel<<<blocks, 256, 0, s>>>(x, count, (float*)x_t);
+    return launch_check(cudaGetLastError(), "round_rows");
+}
+
+// RMS norm with ONE gain: v = mult * gain * (y + bias) / sqrt(mean((y + bias)^2) + eps) [+ res].  One block per row; the row is kept in
+// registers between the two passes (up to SN_PER values per thread, re-read beyond that).
+constexpr int SN_THREADS = 256, SN_PER = 8;
+template <typename T>
+__global__ void __launch_bounds__(SN_THREADS) scalar_rmsnorm_kernel(const float* __restrict__ y, int ldy, const T* __restrict__ bias, const T* __restrict__ gain, float mult,
+                                                                    float eps, int W, const float* res, float* out, int ldo, T* __restrict__ out_t, int ldt,
+                                                                    const int32_t* __restrict__ rows) {
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    const int src = rows ? rows[i] : i;
+    const float* yr = y + (size_t)src * ldy;
+    float v[SN_PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int t = 0; t < SN_PER; ++t) {
+        const int c = threadIdx.x + t * SN_THREADS;
+        v[t] = c < W ? yr[c] + (bias ? to_f(bias[c]) : 0.f) : 0.f;
+        ss = fmaf(v[t], v[t], ss);
+    }
+    for (int c = threadIdx.x + SN_PER * SN_THREADS; c < W; c += SN_THREADS) { const float u = yr[c] + (bias ? to_f(bias[c]) : 0.f); ss = fmaf(u, u, ss); }
+    ss = block_sum(ss, scratch);
+    const float k = mult * to_f(gain[0]) / sqrtf(ss / (float)W + eps);
+#pragma unroll
+    for (int t = 0; t < SN_PER; ++t) {
+        const int c = threadIdx.x + t * SN_THREADS;
+        if (c < W) {
+            float u = v[t] * k;
+            if (res) u += res[(size_t)src * ldo + c];
+            if (out) out[(size_t)i * ldo + c] = u;
+            if (out_t) out_t[(size_t)i * ldt + c] = from_f<T>(u);
+        }
+    }
+    for (int c = threadIdx.x + SN_PER * SN_THREADS; c < W; c += SN_THREADS) {
+        float u = (yr[c] + (bias ? to_f(bias[c]) : 0.f)) * k;
+        if (res) u += res[(size_t)src * ldo + c];
+        if (out) out[(size_t)i * ldo + c] = u;
+        if (out_t) out_t[(size_t)i * ldt + c] = from_f<T>(u);
+    }
+}
+
+int launch_scalar_rmsnorm(int dt, const float* y, int ldy, const void* bias, const void* gain, float mult, float eps, int n, int W, const float* res, float* out,
+                          int ldo, void* out_t, int ldt, const int32_t* rows, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (res && rows && out == res) { set_error("scalar_rmsnorm: gathered rows cannot be added in place"); return WF_ERR_INVALID; }
+    if (dt == WF_BF16) scalar_rmsnorm_kernel<<<n, SN_THREADS, 0, s>>>(y, ldy, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)gain, mult, eps, W, res, out, ldo, (__nv_bfloat16*)out_t, ldt, rows);
+    else scalar_rmsnorm_kernel<<<n, SN_THREADS, 0, s>>>(y, ldy, (const float*)bias, (const float*)gain, mult, eps, W, res, out, ldo, (float*)out_t, ldt, rows);
+    return launch_check(cudaGetLastError(), "scalar_rmsnorm");
+}
+
+// y[i, :] += bias
+template <typename T>
+__global__ void add_bias_kernel(float* __restrict__ y, int ld, const T* __restrict__ bias, int W) {
+    for (int c = threadIdx.x; c < W; c += blockDim.x) y[(size_t)blockIdx.x * ld + c] += to_f(bias[c]);
+}
+
+int launch_add_bias(int dt, float* y, int ld, const void* bias, int n, int W, cudaStream_t s) {
+    if (n <= 0 || !bias) return WF_OK;
+    if (dt == WF_BF16) add_bias_kernel<<<n, 256, 0, s>>>(y, ld, (const __nv_bfloat16*)bias, W);
+    else add_bias_kernel<<<n, 256, 0, s>>>(y, ld, (const float*)bias, W);
+    return launch_check(cudaGetLastError(), "add_bias");
+}
+
 // one block per (row, group)
 template <typename T>
 __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int ldx, const T* __restrict__ w, int gw, float eps, const float* res,

@@ -9,13 +9,11 @@ config.json keys read here: architecture, vocab, width, norm.{eps,groups}, canon
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, List
 
-import numpy as np
-
-from wf_bitnet import _lib, checkpoint
+from wf_bitnet import _lib
 from wf_bitnet._lib import SeqConfig, SeqLayer
-from wf_bitnet.seq_engine import SeqEngine
+from wf_bitnet.seq_model import SeqCausalLM
 
 NO_WINDOW = 1 << 30
 
@@ -38,6 +36,10 @@ class KarusunConfig:
         if not out.layers:
             raise ValueError("config: 'layers' is empty")
         return out
+
+    def fill_native(self, nc: SeqConfig) -> None:
+        nc.block_form = _lib.WF_SEQ_BLOCK_SANDWICH
+        nc.norm_groups, nc.canon_taps = self.norm_groups, self.canon_taps
 
     def native_layers(self) -> List[SeqLayer]:
         res = []
@@ -63,7 +65,7 @@ class KarusunConfig:
                 if f.get("kind", "moe") != "moe":
                     raise ValueError(f"config: layer {i} has unknown feed-forward kind {f.get('kind')!r}")
                 r = f["router"]
-                s.has_ff = 1
+                s.has_ff = _lib.WF_SEQ_FF_ROUTED
                 s.experts, s.identity, s.top = int(r["experts"]), int(r.get("identity", 0)), int(r["top"])
                 g = r.get("groups") or {}
                 s.groups, s.keep = int(g.get("count", 1)), int(g.get("keep", g.get("count", 1)))
@@ -72,85 +74,18 @@ class KarusunConfig:
         return res
 
 
-class KarusunForCausalLM:
-    """Model class of the registry: owns a native engine sized for `max_tokens` cached tokens and `slots` live sequences."""
+class KarusunForCausalLM(SeqCausalLM):
+    """Model class of the registry (weights, engine and step interface: wf_bitnet.seq_model.SeqCausalLM)."""
 
     architecture_names = ("Karusun", "KarusunForCausalLM")
-    min_page_size = 1
 
-    def __init__(self, config: Dict, *, dtype: str = "bfloat16", max_tokens: int = 4096, slots: int = 4, page_size: int = 16,
-                 max_step_tokens: int = 1024, build: bool = False):
-        if dtype not in ("bfloat16", "float32"):
-            raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}")
-        self.config = KarusunConfig.from_dict(config)
-        c = self.config
-        self.dtype = dtype
-        self.page_size = page_size
-        pages = max(1, (max_tokens + page_size - 1) // page_size)
-        self.native_config = SeqConfig(_lib.WF_SEQ_F32 if dtype == "float32" else _lib.WF_SEQ_BF16, c.vocab, c.width, len(c.layers), c.eps,
-                                       c.norm_groups, c.canon_taps, page_size, pages, slots, max_step_tokens)
-        self.engine = SeqEngine(self.native_config, c.native_layers(), build=build)
-        self.vocab = c.vocab
-        self.max_step_tokens = max_step_tokens
+    @staticmethod
+    def read_config(config: Dict) -> KarusunConfig:
+        return KarusunConfig.from_dict(config)
 
-    @classmethod
-    def from_pretrained(cls, model_dir, config=None, **serving):
-        """Model folder (config.json + model.safetensors) -> a loaded model; `serving`: dtype, max_tokens, slots, page_size,
-        max_step_tokens, build."""
-        from pathlib import Path
-        cfg = config if config is not None else checkpoint.read_config(model_dir)
-        m = cls(cfg, **serving)
-        m.load_safetensors(Path(model_dir) / "model.safetensors")
-        return m
-
-    # ---- weights
-    def load_weights(self, weights: Iterable[Tuple[str, np.ndarray, str]]) -> None:
-        """weights: (checkpoint name, array, safetensors dtype string) — bfloat16 as uint16 bit patterns (wf_bitnet.checkpoint)."""
-        wanted = {n for n, _, _ in self.engine.expected_tensors()}
-        for name, a, dt in weights:
-            if name not in wanted:
-                continue
-            self.engine.set_tensor(name, checkpoint.to_float32(a, dt) if self.dtype == "float32" else checkpoint.to_bfloat16_bits(a, dt))
-        # tensors of parts the configuration does not mention are neutral: no input convolution (zero taps), no choice correction
-        for n, count, loaded in self.engine.expected_tensors():
-            if not loaded and ((not self.config.has_canon and n.endswith((".canon1", ".canon2"))) or n.endswith(".mlp.correction")):
-                self.engine.set_tensor(n, np.zeros(count, dtype=np.float32 if self.dtype == "float32" else np.uint16))
-        missing = [n for n, _, loaded in self.engine.expected_tensors() if not loaded]
-        if missing:
-            raise KeyError(f"checkpoint lacks {len(missing)} tensors, first: {missing[:4]}")
-        self.engine.finalize()
-
-    def load_safetensors(self, path) -> None:
-        f = checkpoint.SafetensorsFile(path)
-        try:
-            self.load_weights(f.items())
-        finally:
-            f.close()
-
-    # ---- the step interface the scheduler and the trace replay drive
-    def admit(self) -> int:
-        return self.engine.admit()
-
-    def release(self, slot: int) -> None:
-        self.engine.release(slot)
-
-    def free_pages(self) -> int:
-        return self.engine.free_pages()
-
-    def free_slots(self) -> int:
-        return self.engine.free_slots()
-
-    def pages_for(self, tokens: int) -> int:
-        return (tokens + self.page_size - 1) // self.page_size
-
-    def step(self, slots: Sequence[int], counts: Sequence[int], tokens: Sequence[int], want: Sequence[int] = (), fetch: bool = True):
-        return self.engine.step(slots, counts, tokens, want, fetch)
-
-    def sample(self, nrows: int, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, uniforms=None) -> np.ndarray:
-        return self.engine.sample(nrows, temperature, top_k, top_p, uniforms)
-
-    def close(self) -> None:
-        self.engine.close()
+    def neutral_tensor(self, name: str) -> bool:
+        # parts the configuration does not mention are neutral: no input convolution (zero taps), no choice correction
+        return (not self.config.has_canon and name.endswith((".canon1", ".canon2"))) or name.endswith(".mlp.correction")
 
 
 EntryClass = KarusunForCausalLM

@@ -112,7 +112,10 @@ _lib = None
 # ---- libwf_seq.so (include/wf_seq.h): the engine for layer-stack sequence models ------------------------------------------------
 SEQ_LIB_PATH = Path(os.environ.get("WF_SEQ_LIB", _PKG_ROOT / "libwf_seq.so"))
 WF_SEQ_F32, WF_SEQ_BF16 = 0, 1
-WF_SEQ_LATENT_ATTENTION, WF_SEQ_DELTA = 0, 1
+WF_SEQ_LATENT_ATTENTION, WF_SEQ_DELTA, WF_SEQ_GQA_ATTENTION = 0, 1, 2
+WF_SEQ_BLOCK_SANDWICH, WF_SEQ_BLOCK_POST = 0, 1
+WF_SEQ_FF_NONE, WF_SEQ_FF_ROUTED, WF_SEQ_FF_DENSE = 0, 1, 2
+WF_SEQ_ACT_SILU, WF_SEQ_ACT_CLAMPED = 0, 1
 
 
 class SeqLayer(C.Structure):
@@ -123,7 +126,18 @@ class SeqLayer(C.Structure):
         ("kv_heads", C.c_int), ("conv", C.c_int),
         ("has_ff", C.c_int), ("experts", C.c_int), ("identity", C.c_int), ("top", C.c_int), ("groups", C.c_int), ("keep", C.c_int),
         ("ff", C.c_int),
+        ("qk_norm", C.c_int), ("v_norm", C.c_int), ("proj_bias", C.c_int), ("head_gate", C.c_int), ("kv_from", C.c_int),
+        ("dist_exp", C.c_float),
+        ("ff_act", C.c_int), ("ff_limit", C.c_float), ("router_act", C.c_int), ("group_top", C.c_int), ("router_norm", C.c_int),
+        ("router_scale", C.c_float), ("shared_ff", C.c_int), ("shared_limit", C.c_float),
     ]
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        if "kv_from" not in kw:
+            self.kv_from = -1
+        if "router_scale" not in kw:
+            self.router_scale = 1.0
 
 
 class SeqConfig(C.Structure):
@@ -131,6 +145,7 @@ class SeqConfig(C.Structure):
         ("dtype", C.c_int), ("vocab", C.c_int), ("width", C.c_int), ("n_layers", C.c_int), ("eps", C.c_float),
         ("norm_groups", C.c_int), ("canon_taps", C.c_int), ("page_size", C.c_int), ("max_pages", C.c_int), ("slots", C.c_int),
         ("max_step_tokens", C.c_int),
+        ("block_form", C.c_int), ("residual_mult", C.c_float), ("pos_embed", C.c_int), ("pos_base", C.c_float),
     ]
 
 

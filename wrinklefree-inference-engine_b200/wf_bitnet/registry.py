@@ -15,6 +15,8 @@ _MODULES: Dict[str, str] = {
     "BitnetForCausalLM": "sglang.srt.models.bitnet",
     "Karusun": "sglang.srt.models.karusun",
     "KarusunForCausalLM": "sglang.srt.models.karusun",
+    "Tutizen": "sglang.srt.models.tutizen",
+    "TutizenForCausalLM": "sglang.srt.models.tutizen",
 }
 
 
