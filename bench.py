@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """bench.py — decode throughput of the BitNet-2B-4T-shaped hot path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload bs64|bs1|hybrid]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload bs64|bs1|hybrid|tutizen]
 
 --workload hybrid (1 GPU) measures the layer-stack sequence engine (latent attention / gated delta rule / routed feed-forward) instead:
 prefill and decode tok/s at two layer sizes with random weights, per launch-group times, and the BitNet engine at equal size beside it.
@@ -901,23 +901,119 @@ def run_hybrid(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------------------------
+# --workload tutizen: the Tutizen design (grouped-query attention with shared caches, clamped gated units dense / routed with a shared
+# expert) on the sequence engine, at sizes that resemble real layers, random weights, beside the closest existing model on the same
+# engine at equal width / heads / layers / experts: Karusun with latent-attention layers and its routed feed-forward.
+TUTIZEN_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, d=128, dv=128, experts=30, top=6, groups=5, keep=3, ff=384, vocab=32768, layers=4,
+                  lat=dict(d=64, r=32, dv=64, R=256)),
+    "w2560": dict(width=2560, heads=20, kv_heads=5, d=128, dv=128, experts=30, top=6, groups=5, keep=3, ff=1152, vocab=128256, layers=4,
+                  lat=dict(d=96, r=32, dv=128, R=512)),
+}
+
+
+def tutizen_config(z):
+    def att(src=None):
+        m = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["d"], "vdim": z["dv"], "scale": z["d"] ** -0.5}
+        if src is not None:
+            m["kv_from"] = src
+        return {"type": "attention", "mixer": m}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0}, "shared": {"ff": z["ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    dense = {"kind": "dense", "ff": z["top"] * z["ff"], "limit": 7.0}
+    layers = []
+    for i in range(z["layers"]):            # pairs: a layer with its own keys / values, then one that reads them
+        layers.append(dict(att(None if i % 2 == 0 else i - 1), mlp=dense if i % 4 == 2 else moe))
+    return {"architecture": "Tutizen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.5, "layers": layers}
+
+
+def karusun_attention_config(z):
+    t = z["lat"]
+    lat = {"type": "latent_attention", "mixer": {"heads": z["heads"], "dim": t["d"], "rot_dim": t["r"], "vdim": t["dv"], "kv_rank": t["R"],
+                                                  "rot": {"base": 10000.0, "dims": t["r"]}, "scale": (t["d"] + t["r"]) ** -0.5}}
+    ff = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "identity": 0, "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    return {"architecture": "Karusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5, "groups": 4}, "canon": {"taps": 4},
+            "layers": [dict(lat, mlp=ff) for _ in range(z["layers"])]}
+
+
+def measure_seq_model(cfg, prompt, decode_points, K):
+    """prefill of one prompt from an empty cache and decode steps at (batch, context) points, CUDA-event times on the engine's stream
+    (decode steps as graph replays), plus the per-launch-group profile of the prompt and of the smallest and largest decode point."""
+    max_b = max(b for b, _ in decode_points)
+    tokens_cap = max(max(b * (c + 16) for b, c in decode_points), prompt + 16)
+    m = hybrid_model(cfg, tokens_cap, max_b, prompt)
+    slots = [m.admit() for _ in range(max_b)]
+    res, launches = {}, 0
+    ms = m.engine.time_step(slots[:1], [prompt], iters=K)
+    res["prefill"] = {"tokens": prompt, "ms": round(ms, 3), "tok_s": round(prompt / ms * 1e3, 1)}
+    res["prefill_profile_ms"] = {k: round(v[0], 4) for k, v in m.engine.profile_step(slots[:1], [prompt], iters=2).items()}
+    launches += (K + 2) * m.engine.launches_last_step()
+    res["decode"] = {}
+    for b, ctx in decode_points:
+        for s_ in slots[:b]:
+            m.engine.set_length(s_, ctx)
+        ms = m.engine.time_step(slots[:b], [1] * b, iters=max(K, 10))
+        res["decode"][f"bs{b}_ctx{ctx}"] = {"ms": round(ms, 4), "tok_s": round(b / ms * 1e3, 1), "launches_per_step": m.engine.launches_last_step()}
+        launches += (max(K, 10) + 2) * m.engine.launches_last_step()
+        if b in (1, max_b):
+            res[f"decode_profile_ms_bs{b}"] = {k: round(v[0], 4) for k, v in m.engine.profile_step(slots[:b], [1] * b, iters=3).items()}
+    res["device_bytes"] = m.engine.device_bytes()
+    m.close()
+    return res, launches
+
+
+def run_tutizen(args):
+    from wf_bitnet import _lib
+    torch.cuda.set_device(0)
+    _lib.require_gpu()
+    K, W_ = max(2, args.steps), max(3, args.warmup)
+    peak, peak_src = measured_peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
+    out, launches = {}, 0
+    for name, z in TUTIZEN_SIZES.items():
+        if args.hybrid_size and name != args.hybrid_size:
+            continue
+        prompt = 2048
+        decode_points = [(1, 512), (8, 2048), (64, 4096)] if name == "w2560" else [(1, 512), (8, 1024), (64, 1024)]
+        cfg = tutizen_config(z)
+        res, n1 = measure_seq_model(cfg, prompt, decode_points, K)
+        res["layer_kinds"] = [("attention" if "kv_from" not in L["mixer"] else f"attention(kv of layer {L['mixer']['kv_from']})") + " + " + L["mlp"]["kind"] for L in cfg["layers"]]
+        # bytes of cached keys and values one decoded token reads per attention layer and per 1000 tokens of context
+        res["kv_bytes_per_layer_per_1k_ctx"] = 1000 * z["kv_heads"] * (z["d"] + z["dv"]) * 2
+        kres, n2 = measure_seq_model(karusun_attention_config(z), prompt, decode_points, K)
+        res["karusun_equal_size"] = kres
+        launches += n1 + n2
+        out[name] = res
+    clocks = sampler.stop()
+    head = out.get("w2560") or next(iter(out.values()))
+    top = sorted(head["decode"].items())[-1]
+    emit({"metric": "prefill / decode tok/s of the Tutizen design on the sequence engine beside Karusun (latent attention) at equal size", "workload": "tutizen",
+          "value": top[1]["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W_, "higher_is_better": True, "dtype": "bf16",
+          "data": "synthetic (random weights; decode contexts are whatever the cache pages hold)", "vs_baseline": None,
+          "config": {"model": "Tutizen-shaped, " + ", ".join(out), "point": top[0], "l2": "weights per step exceed L2 (126 MB) at w2560; w1024 is L2-resident"},
+          "hbm_peak_gbs": peak, "peak_source": peak_src, "sizes": out, "clocks": clocks, "gpu_launches": launches})
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="bs64", choices=["bs64", "bs1", "hybrid"] + sorted(TP_WORKLOADS))
-    ap.add_argument("--hybrid-size", default="", help="--workload hybrid: run only this size (w1024 | w2560)")
+    ap.add_argument("--workload", default="bs64", choices=["bs64", "bs1", "hybrid", "tutizen"] + sorted(TP_WORKLOADS))
+    ap.add_argument("--hybrid-size", default="", help="--workload hybrid / tutizen: run only this size (w1024 | w2560)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-aux", action="store_true", help="skip the batch-1 aux measurement")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel suite (aux.tp)")
     args = ap.parse_args()
-    if args.workload == "hybrid":
+    if args.workload in ("hybrid", "tutizen"):
         if args.impl == "reference":
             emit({"impl": "reference", "unavailable": "the reference has no model of this design; its arm is defined for the 2B workloads only"})
             return 0
-        return run_hybrid(args)
+        return run_hybrid(args) if args.workload == "hybrid" else run_tutizen(args)
     if args.workload in TP_WORKLOADS:
         if args.impl == "reference":
             emit({"impl": "reference", "unavailable": "the reference arm is defined for the 2B workloads (bs64 / bs1) only"})

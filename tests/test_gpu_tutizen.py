@@ -367,7 +367,7 @@ def test_far_key_among_hundreds(dtype, far):
     want = O.attention(torch.from_numpy(x).double(), P, mx, 1e-5)[0].numpy()
     blind = x.copy()
     blind[far, :16] = 0
-    assert rel_err(O.attention(torch.from_numpy(blind).double(), P, mx, 1e-5)[0].numpy()[-1:], want[-1:])[0] > 0.3
+    assert rel_err(O.attention(torch.from_numpy(blind).double(), P, mx, 1e-5)[0].numpy()[-1:], want[-1:])[0] > 0.1
     m = build(cfg, w, dtype, max_tokens=512, slots=2, page_size=64, max_step_tokens=256)
     s = m.admit()
     got, a = [], 0
@@ -377,6 +377,38 @@ def test_far_key_among_hundreds(dtype, far):
     err = rel_err(np.concatenate(got), want)
     assert err[-1] < (TOL[dtype] if dtype == "float32" else 2e-2), err[-1]
     assert err.max() < (TOL[dtype] if dtype == "float32" else 5e-2)
+    m.close()
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(8, 2, 64, 64), (3, 3, 128, 128), (16, 1, 32, 96), (12, 4, 72, 40), (2, 1, 8, 24)])
+def test_attention_on_tensor_cores_prompts_decoding_and_key_splits(heads, kv_heads, dim, vdim):
+    """Sizes the tensor-core kernel takes (group sizes 1, 3, 4, 16 and 2; per-head sizes that fill or do not fill its 64 / 128 wide tiles):
+    three sequences of unequal length read as prompt portions in one ragged batch (the prompt form, tiles that end inside a sequence), then
+    decoded together one token each for a few steps in a pool large enough that the key range is cut over several CTAs (the decode form
+    with its merge), all against the oracle."""
+    cfg = config([attn(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=2.0 / math.sqrt(dim))], width=64, vocab=20)
+    w = make_weights(cfg, 121)
+    P, mx = t64(O.sub(w, "l0.mix.")), cfg["layers"][0]["mixer"]
+    lens = (333, 70, 129)
+    xs = [_rows(n + 4, 64, 122 + n) for n in lens]
+    want = [O.attention(torch.from_numpy(x).double(), P, mx, 1e-5)[0].numpy() for x in xs]
+    m = build(cfg, w, "bfloat16", max_tokens=4096, slots=4, page_size=16, max_step_tokens=512)
+    slots = [m.admit() for _ in lens]
+    got = [[] for _ in lens]
+    fed = [0, 0, 0]
+    for counts in ((200, 70, 100), (133, 0, 29)):
+        act = [k for k in range(3) if counts[k]]
+        out = m.engine.run_part(0, 2, [slots[k] for k in act], [counts[k] for k in act], np.concatenate([xs[k][fed[k]:fed[k] + counts[k]] for k in act]))
+        a = 0
+        for k in act:
+            got[k].append(out[a:a + counts[k]]); a += counts[k]; fed[k] += counts[k]
+    for _ in range(4):
+        out = m.engine.run_part(0, 2, slots, [1, 1, 1], np.stack([xs[k][fed[k]] for k in range(3)]))
+        for k in range(3):
+            got[k].append(out[k:k + 1]); fed[k] += 1
+    for k in range(3):
+        err = rel_err(np.concatenate(got[k]), want[k])
+        assert err.max() < 3e-2, (k, int(err.argmax()), err.max())
     m.close()
 
 

@@ -8,6 +8,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <algorithm>
 #include <map>
 #include <string>
 #include <vector>
@@ -85,6 +86,8 @@ struct wf_seq_engine {
     int fuse_input = 1;               // norm + input convolution (+ state roll of single-token sequences) in one kernel (WF_SEQ_FUSE_INPUT=0: three kernels)
     int attn_mma = 2;                 // latent attention on tensor cores where the sizes allow it: 2 keys-as-rows form first, 1 heads-as-rows form only, 0 plain kernel (WF_SEQ_ATTN_MMA)
     float* row_inv = nullptr;         // [max_step_tokens][norm groups] row statistics of the many-token input kernel
+    float* gqa_ws = nullptr;          // partial results of key-split grouped-query attention: gqa_ws_rows (token, head, split) rows
+    int gqa_ws_rows = 0;
     float* attn_ws = nullptr;         // partial results of key-split attention
     int attn_ws_rows = 0;             // token-splits it holds
     int pair_path_max = 64;           // up to this many (token, expert) pairs the experts run as per-pair weight streams (WF_SEQ_PAIR_MAX)
@@ -337,7 +340,22 @@ int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b) {
     mark(e, "attn.proj_gemm");
     if ((rc = launch_gqa_prep(e->dt, b, D, e->proj, L.np, L.k_off, L.v_off, L.g_off, L.qb, L.kb, L.vb, e->cfg.eps, pc, e->qn, c.head_gate ? e->gate : nullptr, s))) return rc;
     mark(e, "attn.prep+kv_write");
-    if ((rc = launch_gqa_attn(e->dt, b, D, e->qn, c.head_gate ? e->gate : nullptr, pc, e->og, s))) return rc;
+    const float* gate = c.head_gate ? e->gate : nullptr;
+    if (e->dt == WF_BF16 && e->attn_mma >= 1 && gqa_attn_mma_usable(D, pc)) {
+        // decoding (one token per sequence): few CTAs and long key ranges, so the keys are cut until a resident wave covers the machine.
+        // The cut depends on the batch size and the pool only, never on the lengths: a captured step stays valid.
+        int splits = 1;
+        if (n == b.nseq) {
+            const long long span = std::min<long long>(c.window, (long long)e->cfg.max_pages * e->cfg.page_size);
+            const int ctas = n * c.kv_heads, resident = 2 * sm_count();
+            splits = resident / ctas;
+            if (splits > span / 256) splits = (int)(span / 256);
+            if (splits > e->gqa_ws_rows / (n * c.heads)) splits = e->gqa_ws_rows / (n * c.heads);
+            if (splits > 16) splits = 16;
+            if (splits < 1) splits = 1;
+        }
+        if ((rc = launch_gqa_attn_mma(b, D, e->qn, gate, pc, e->og, e->gqa_ws, splits, s))) return rc;
+    } else if ((rc = launch_gqa_attn(e->dt, b, D, e->qn, gate, pc, e->og, s))) return rc;
     mark(e, "attn.attention");
     rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
     mark(e, "attn.out_gemm");
@@ -596,7 +614,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     add_tensor(e, "final.norm", e->final_norm, norm_elems);
     add_tensor(e, "head", e->head, (size_t)c.vocab * W);
     // maxima over layers for the shared workspaces
-    size_t max_np = 1, max_hd = 1, max_hr = 1, max_hrot = 1, max_hv = 1, max_C = 1, max_H = 1, max_N = 1, max_top = 1, max_E = 1, max_ff = 1, max_uff = 0;
+    size_t max_np = 1, max_hd = 1, max_hr = 1, max_hrot = 1, max_hv = 1, max_C = 1, max_H = 1, max_N = 1, max_top = 1, max_E = 1, max_ff = 1, max_uff = 0, max_gqa_dv = 0;
     long long cache_elems = 0;
     size_t st = 0;
     e->layers.resize(c.n_layers);
@@ -650,7 +668,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
                 L.cache_off = cache_elems;
                 cache_elems += (long long)c.page_size * (nk + nvk);
             }
-            max_hd = std::max(max_hd, nq);
+            max_hd = std::max(max_hd, nq); max_gqa_dv = std::max(max_gqa_dv, (size_t)l.vdim);
         } else if (l.type == WF_SEQ_LATENT_ATTENTION) {
             const size_t nq = (size_t)l.heads * (l.dim + l.rot_dim), nkv = l.kv_rank + l.rot_dim;
             L.np = (int)(nq + nkv + nv);
@@ -748,6 +766,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     e->attn_ws_rows = 4 * 148;
     if (e->dt == WF_BF16 && max_hr > 1) TRY(dalloc_bytes(e, (void**)&e->attn_ws, (size_t)e->attn_ws_rows * (max_hr + 2 * max_H) * sizeof(float)));
     TRY(dalloc_n(e, &e->gate, (size_t)T * max_H));
+    if (e->dt == WF_BF16 && max_gqa_dv) { e->gqa_ws_rows = 8192; TRY(dalloc_bytes(e, (void**)&e->gqa_ws, gqa_attn_mma_workspace(e->gqa_ws_rows, 1, (int)max_gqa_dv))); }
     if (max_uff) { TRY(dalloc_n(e, &e->ugu, (size_t)T * 2 * max_uff)); TRY(dalloc_t(e, &e->uhmid, (size_t)T * max_uff)); TRY(dalloc_n(e, &e->uy, (size_t)T * W)); }
     TRY(dalloc_n(e, &e->qkvc, (size_t)T * max_C)); TRY(dalloc_n(e, &e->beta, (size_t)T * max_H)); TRY(dalloc_n(e, &e->decay, (size_t)T * max_H));
     TRY(dalloc_n(e, &e->od, (size_t)T * max_hv));

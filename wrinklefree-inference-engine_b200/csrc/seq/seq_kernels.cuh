@@ -115,6 +115,14 @@ int launch_gqa_prep(int dt, const Batch& b, const GqaDims& D, const float* proj,
 // sum, times gate[n, H] (null: no gate).
 int launch_gqa_attn(int dt, const Batch& b, const GqaDims& D, const void* qn, const float* gate, const PagedCache& pc, void* out, cudaStream_t s);
 
+// the same on tensor cores (bf16 storage only; seq_attn_mma.cu): group sizes up to 16, per-head sizes multiples of 8 up to 128, cache rows
+// 16-byte aligned.  When every sequence brings one token the key range can be cut over `splits` CTAs; that needs a workspace of
+// gqa_attn_mma_workspace(n * H, splits, dv) bytes.
+bool gqa_attn_mma_usable(const GqaDims& D, const PagedCache& pc);
+size_t gqa_attn_mma_workspace(int rows, int splits, int dv);
+int launch_gqa_attn_mma(const Batch& b, const GqaDims& D, const void* qn, const float* gate, const PagedCache& pc, void* out, float* workspace, int splits,
+                        cudaStream_t s);
+
 // ---- gated delta rule ----------------------------------------------------------------------------------------------------
 struct DeltaDims { int H, Hk, d, dv; };
 // in place on qkv float [n, C = 2 * Hk * d + H * dv] (ld): q and k heads -> unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times d^-1/2.
