@@ -2,7 +2,7 @@
 //
 // A CTA of four warps owns one key/value head and a tile of query rows; a row is a (token, query head of that key/value head's group)
 // pair, so one staged key / value tile serves every head of the group.  Keys and values are staged 64 at a time from the paged cache by
-// cp.async into a double buffer (rows padded by 16 bytes: conflict-free ldmatrix).  Scores S = Q K^T, then the distance penalty and the
+// cp.async into a ring of two (prompts) or three (decoding) buffers (rows padded by 16 bytes: conflict-free ldmatrix).  Scores S = Q K^T, then the distance penalty and the
 // causal / window mask, an online softmax in float, and O += P V with the weights entering the product as a TWO-term bf16 split
 // (p = hi + lo, both products accumulated in float), so that the value sum sees the float weights to 2^-17 rather than rounded to bf16.
 //
@@ -59,9 +59,10 @@ __global__ void __launch_bounds__(AM_THREADS) gqa_attn_mma_kernel(Batch b, GqaDi
     constexpr int NVT = DVP / 8;                           // n-tiles of the value product
     constexpr int KW = DECODE ? 16 : AM_KT;                // keys of a tile that one warp consumes
     constexpr int NST = KW / 8;                            // score n-tiles per warp
+    constexpr int NSTAGE = DECODE ? 3 : 2;                 // staged tiles: decoding is a stream of cache rows, two tiles stay in flight
     extern __shared__ __align__(16) unsigned char smraw[];
-    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);           // [2][AM_KT][KS]
-    __nv_bfloat16* Vs = Ks + 2 * AM_KT * KS;                               // [2][AM_KT][VS]
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);           // [NSTAGE][AM_KT][KS]
+    __nv_bfloat16* Vs = Ks + NSTAGE * AM_KT * KS;                          // [NSTAGE][AM_KT][VS]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g4 = lane >> 2, t4 = lane & 3;
     const int kvh = blockIdx.y, split = blockIdx.z;
     const int rep = D.H / D.G;
@@ -141,10 +142,13 @@ __global__ void __launch_bounds__(AM_THREADS) gqa_attn_mma_kernel(Batch b, GqaDi
 #pragma unroll
     for (int j = 0; j < NVT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
     const int kw0 = DECODE ? warp * 16 : 0;                // first key of the tile this warp consumes
-    if (t_lo <= t_hi) stage(t_lo, 0);
+#pragma unroll
+    for (int i = 0; i < NSTAGE - 1; ++i) { if (t_lo + i <= t_hi) stage(t_lo + i, i); else am_commit(); }
     for (int t = t_lo; t <= t_hi; ++t) {
-        const int buf = (t - t_lo) & 1;
-        if (t + 1 <= t_hi) { stage(t + 1, buf ^ 1); am_wait<1>(); } else am_wait<0>();
+        const int buf = (t - t_lo) % NSTAGE;
+        // the tile NSTAGE - 1 ahead goes into the buffer that the previous iteration finished reading (an empty group keeps the count uniform)
+        if (t + NSTAGE - 1 <= t_hi) stage(t + NSTAGE - 1, (t - t_lo + NSTAGE - 1) % NSTAGE); else am_commit();
+        am_wait<NSTAGE - 1>();
         __syncthreads();
         const uint32_t kb = smem_u32(Ks + (size_t)buf * AM_KT * KS), vb = smem_u32(Vs + (size_t)buf * AM_KT * VS);
         // ---- scores
@@ -226,8 +230,9 @@ __global__ void __launch_bounds__(AM_THREADS) gqa_attn_mma_kernel(Batch b, GqaDi
                 am_mma(o[2 * np + 1], pl, vf[2], vf[3]);
             }
         }
-        __syncthreads();                                   // the buffer is staged again two tiles on
+        __syncthreads();                                   // the buffer is staged again in the next iteration
     }
+    am_wait<0>();
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
         l_run[k] += __shfl_xor_sync(0xffffffffu, l_run[k], 1);
@@ -313,7 +318,7 @@ __global__ void gqa_attn_merge_kernel(int rows, int splits, int dv, const float*
 
 template <int DKP, int DVP, bool DECODE>
 int am_launch(const Batch& b, const GqaDims& D, const void* qn, const float* gate, const PagedCache& pc, void* out, const AmParams& ap, int tiles, cudaStream_t s) {
-    size_t smem = (size_t)2 * AM_KT * ((DKP + 8) + (DVP + 8)) * sizeof(__nv_bfloat16);
+    size_t smem = (size_t)(DECODE ? 3 : 2) * AM_KT * ((DKP + 8) + (DVP + 8)) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(128 + 64 * DVP) * sizeof(float);
     if (DECODE && merge > smem) smem = merge;
     static bool attr_set = false;
