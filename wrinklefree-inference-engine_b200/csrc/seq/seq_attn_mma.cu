@@ -13,6 +13,7 @@
 //     through a float workspace and a merge kernel.
 #include "seq_kernels.cuh"
 #include <math.h>
+#include <stdlib.h>
 
 namespace wf {
 namespace seq {
@@ -47,19 +48,19 @@ struct AmParams {
     int rp2, rp2_log;        // rows per token: the group size rounded up to a power of two
     int tq;                  // tokens per CTA tile
     int splits;              // key splits (decode form)
+    int ps_log;              // log2 of the page size when that is a power of two, else -1
     float* part;             // splits > 1: [n * H][splits][dv + 2] (weighted values unnormalised, max, sum)
 };
 
-// DKP / DVP: per-head key and value sizes rounded up to 64 or 128.  DECODE: the decode form.
-template <int DKP, int DVP, bool DECODE>
-__global__ void __launch_bounds__(AM_THREADS) gqa_attn_mma_kernel(Batch b, GqaDims D, const __nv_bfloat16* __restrict__ qn, const float* __restrict__ gate,
+// DKP / DVP: per-head key and value sizes rounded up to 64 or 128.  DECODE: the decode form.  NSTAGE: staged tiles (ring depth).
+template <int DKP, int DVP, bool DECODE, int NSTAGE>
+__global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, GqaDims D, const __nv_bfloat16* __restrict__ qn, const float* __restrict__ gate,
                                                                     PagedCache pc, __nv_bfloat16* __restrict__ out, AmParams ap) {
     constexpr int KS = DKP + 8, VS = DVP + 8;              // shared-memory row strides in elements
     constexpr int NKS = DKP / 16;                          // k-steps of the score product
     constexpr int NVT = DVP / 8;                           // n-tiles of the value product
     constexpr int KW = DECODE ? 16 : AM_KT;                // keys of a tile that one warp consumes
     constexpr int NST = KW / 8;                            // score n-tiles per warp
-    constexpr int NSTAGE = DECODE ? 3 : 2;                 // staged tiles: decoding is a stream of cache rows, two tiles stay in flight
     extern __shared__ __align__(16) unsigned char smraw[];
     __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);           // [NSTAGE][AM_KT][KS]
     __nv_bfloat16* Vs = Ks + NSTAGE * AM_KT * KS;                          // [NSTAGE][AM_KT][VS]
@@ -69,7 +70,8 @@ __global__ void __launch_bounds__(AM_THREADS) gqa_attn_mma_kernel(Batch b, GqaDi
     // which sequence and which of its tokens this tile holds
     int sq = -1, tok0 = 0, ntok = 0;
     {
-        int t = blockIdx.x;
+        // prompt form: the last tiles of a sequence see the most keys, so they are handed out first and the short ones fill the tail
+        int t = DECODE ? (int)blockIdx.x : (int)(gridDim.x - 1 - blockIdx.x);
         for (int s = 0; s < b.nseq; ++s) {
             const int tiles = (b.seq_len[s] + ap.tq - 1) / ap.tq;
             if (t < tiles) { sq = s; tok0 = t * ap.tq; ntok = b.seq_len[s] - tok0 < ap.tq ? b.seq_len[s] - tok0 : ap.tq; break; }
@@ -117,23 +119,47 @@ __global__ void __launch_bounds__(AM_THREADS) gqa_attn_mma_kernel(Batch b, GqaDi
     }
     const size_t k_base = (size_t)kvh * pc.page_size * D.d, v_base = (size_t)D.G * pc.page_size * D.d + (size_t)kvh * pc.page_size * D.dv;
     const __nv_bfloat16* pool = (const __nv_bfloat16*)pc.pool + pc.layer_off;
+    // a thread stages the same 16-byte column of every row it touches: 128 threads cover 128 / (row chunks) rows per pass
+    constexpr int KC = DKP / 8, VC = DVP / 8;              // 16-byte chunks per row
+    constexpr int KR = AM_THREADS / KC, VR = AM_THREADS / VC;
+    const int kpart = tid % KC, krow = tid / KC, vpart = tid % VC, vrow = tid / VC;
+    const bool kcol_ok = kpart * 8 < D.d, vcol_ok = vpart * 8 < D.dv;
+    const size_t koff = k_base + kpart * 8, voff = v_base + vpart * 8;
+    auto page_of = [&](int j, int& slot) -> const __nv_bfloat16* {      // the layer's part of the page that holds key j, and j's slot in it
+        int pg;
+        if (ap.ps_log >= 0) { pg = j >> ap.ps_log; slot = j & (pc.page_size - 1); } else { pg = j / pc.page_size; slot = j - pg * pc.page_size; }
+        return pool + (size_t)bt[pg] * pc.page_stride;
+    };
     auto stage = [&](int t, int buf) {
         const int j0 = t * AM_KT;
-        constexpr int KC = DKP / 8, VC = DVP / 8;          // 16-byte chunks per row
         const uint32_t kd = smem_u32(Ks + (size_t)buf * AM_KT * KS), vd = smem_u32(Vs + (size_t)buf * AM_KT * VS);
-        for (int c = tid; c < AM_KT * KC; c += AM_THREADS) {
-            const int key = c / KC, part = c % KC, j = j0 + key;
-            const bool ok = j <= pos_last && part * 8 < D.d;
-            const int jj = ok ? j : 0;
-            const __nv_bfloat16* src = pool + (size_t)bt[jj / pc.page_size] * pc.page_stride + k_base + (size_t)(jj % pc.page_size) * D.d + part * 8;
-            am_cp16(kd + (uint32_t)(key * KS + part * 8) * 2u, ok ? src : pool, ok);
-        }
-        for (int c = tid; c < AM_KT * VC; c += AM_THREADS) {
-            const int key = c / VC, part = c % VC, j = j0 + key;
-            const bool ok = j <= pos_last && part * 8 < D.dv;
-            const int jj = ok ? j : 0;
-            const __nv_bfloat16* src = pool + (size_t)bt[jj / pc.page_size] * pc.page_stride + v_base + (size_t)(jj % pc.page_size) * D.dv + part * 8;
-            am_cp16(vd + (uint32_t)(key * VS + part * 8) * 2u, ok ? src : pool, ok);
+        if (KC == VC) {                                    // one page lookup per row serves the key and the value chunk
+#pragma unroll
+            for (int k = 0; k < AM_KT / KR; ++k) {
+                const int key = krow + k * KR, j = j0 + key;
+                const bool ok = j <= pos_last;
+                int slot;
+                const __nv_bfloat16* pg = page_of(ok ? j : 0, slot);
+                am_cp16(kd + (uint32_t)(key * KS + kpart * 8) * 2u, pg + koff + (size_t)slot * D.d, ok && kcol_ok);
+                am_cp16(vd + (uint32_t)(key * VS + vpart * 8) * 2u, pg + voff + (size_t)slot * D.dv, ok && vcol_ok);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < AM_KT / KR; ++k) {
+                const int key = krow + k * KR, j = j0 + key;
+                const bool ok = j <= pos_last;
+                int slot;
+                const __nv_bfloat16* pg = page_of(ok ? j : 0, slot);
+                am_cp16(kd + (uint32_t)(key * KS + kpart * 8) * 2u, pg + koff + (size_t)slot * D.d, ok && kcol_ok);
+            }
+#pragma unroll
+            for (int k = 0; k < AM_KT / VR; ++k) {
+                const int key = vrow + k * VR, j = j0 + key;
+                const bool ok = j <= pos_last;
+                int slot;
+                const __nv_bfloat16* pg = page_of(ok ? j : 0, slot);
+                am_cp16(vd + (uint32_t)(key * VS + vpart * 8) * 2u, pg + voff + (size_t)slot * D.dv, ok && vcol_ok);
+            }
         }
         am_commit();
     };
@@ -316,29 +342,31 @@ __global__ void gqa_attn_merge_kernel(int rows, int splits, int dv, const float*
     }
 }
 
-template <int DKP, int DVP, bool DECODE>
+template <int DKP, int DVP, bool DECODE, int NSTAGE>
 int am_launch(const Batch& b, const GqaDims& D, const void* qn, const float* gate, const PagedCache& pc, void* out, const AmParams& ap, int tiles, cudaStream_t s) {
-    size_t smem = (size_t)(DECODE ? 3 : 2) * AM_KT * ((DKP + 8) + (DVP + 8)) * sizeof(__nv_bfloat16);
+    size_t smem = (size_t)NSTAGE * AM_KT * ((DKP + 8) + (DVP + 8)) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(128 + 64 * DVP) * sizeof(float);
     if (DECODE && merge > smem) smem = merge;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cuda_check(cudaFuncSetAttribute(gqa_attn_mma_kernel<DKP, DVP, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attention shared memory")) return WF_ERR_CUDA;
+        if (cuda_check(cudaFuncSetAttribute(gqa_attn_mma_kernel<DKP, DVP, DECODE, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attention shared memory")) return WF_ERR_CUDA;
         attr_set = true;
     }
     dim3 grid(tiles, D.G, DECODE ? ap.splits : 1);
-    gqa_attn_mma_kernel<DKP, DVP, DECODE><<<grid, AM_THREADS, smem, s>>>(b, D, (const __nv_bfloat16*)qn, gate, pc, (__nv_bfloat16*)out, ap);
+    gqa_attn_mma_kernel<DKP, DVP, DECODE, NSTAGE><<<grid, AM_THREADS, smem, s>>>(b, D, (const __nv_bfloat16*)qn, gate, pc, (__nv_bfloat16*)out, ap);
     return launch_check(cudaGetLastError(), "gqa_attn_mma");
 }
 
-template <bool DECODE>
+template <bool DECODE, int NSTAGE>
 int am_dispatch(const Batch& b, const GqaDims& D, const void* qn, const float* gate, const PagedCache& pc, void* out, const AmParams& ap, int tiles, cudaStream_t s) {
     const bool k64 = D.d <= 64, v64 = D.dv <= 64;
-    if (k64 && v64) return am_launch<64, 64, DECODE>(b, D, qn, gate, pc, out, ap, tiles, s);
-    if (k64) return am_launch<64, 128, DECODE>(b, D, qn, gate, pc, out, ap, tiles, s);
-    if (v64) return am_launch<128, 64, DECODE>(b, D, qn, gate, pc, out, ap, tiles, s);
-    return am_launch<128, 128, DECODE>(b, D, qn, gate, pc, out, ap, tiles, s);
+    if (k64 && v64) return am_launch<64, 64, DECODE, NSTAGE>(b, D, qn, gate, pc, out, ap, tiles, s);
+    if (k64) return am_launch<64, 128, DECODE, NSTAGE>(b, D, qn, gate, pc, out, ap, tiles, s);
+    if (v64) return am_launch<128, 64, DECODE, NSTAGE>(b, D, qn, gate, pc, out, ap, tiles, s);
+    return am_launch<128, 128, DECODE, NSTAGE>(b, D, qn, gate, pc, out, ap, tiles, s);
 }
+
+int g_decode_stages = -1;
 
 }  // namespace
 
@@ -364,7 +392,11 @@ int launch_gqa_attn_mma(const Batch& b, const GqaDims& D, const void* qn, const 
     ap.part = workspace;
     // every sequence's tokens are cut into tiles of tq; n / tq + nseq bounds their number (CTAs beyond the last tile return at once)
     const int tiles = decode ? b.n : b.n / ap.tq + b.nseq;
-    int rc = decode ? am_dispatch<true>(b, D, qn, gate, pc, out, ap, tiles, s) : am_dispatch<false>(b, D, qn, gate, pc, out, ap, tiles, s);
+    ap.ps_log = -1;
+    for (int k = 0; k < 30; ++k) if (pc.page_size == (1 << k)) ap.ps_log = k;
+    if (g_decode_stages < 0) { const char* e = getenv("WF_SEQ_ATTN_STAGES"); g_decode_stages = e && atoi(e) == 3 ? 3 : 2; }
+    int rc = !decode ? am_dispatch<false, 2>(b, D, qn, gate, pc, out, ap, tiles, s)
+                     : (g_decode_stages == 3 ? am_dispatch<true, 3>(b, D, qn, gate, pc, out, ap, tiles, s) : am_dispatch<true, 2>(b, D, qn, gate, pc, out, ap, tiles, s));
     if (rc || ap.splits == 1) return rc;
     const int rows = b.n * D.H;
     gqa_attn_merge_kernel<<<(rows + 3) / 4, 128, 0, s>>>(rows, ap.splits, D.dv, workspace, gate, (__nv_bfloat16*)out);

@@ -86,6 +86,7 @@ struct wf_seq_engine {
     int fuse_input = 1;               // norm + input convolution (+ state roll of single-token sequences) in one kernel (WF_SEQ_FUSE_INPUT=0: three kernels)
     int attn_mma = 2;                 // latent attention on tensor cores where the sizes allow it: 2 keys-as-rows form first, 1 heads-as-rows form only, 0 plain kernel (WF_SEQ_ATTN_MMA)
     float* row_inv = nullptr;         // [max_step_tokens][norm groups] row statistics of the many-token input kernel
+    int attn_waves = 4;               // decode attention: resident waves of CTAs the key splits aim at (WF_SEQ_ATTN_WAVES)
     float* gqa_ws = nullptr;          // partial results of key-split grouped-query attention: gqa_ws_rows (token, head, split) rows
     int gqa_ws_rows = 0;
     float* attn_ws = nullptr;         // partial results of key-split attention
@@ -342,13 +343,14 @@ int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b) {
     mark(e, "attn.prep+kv_write");
     const float* gate = c.head_gate ? e->gate : nullptr;
     if (e->dt == WF_BF16 && e->attn_mma >= 1 && gqa_attn_mma_usable(D, pc)) {
-        // decoding (one token per sequence): few CTAs and long key ranges, so the keys are cut until a resident wave covers the machine.
+        // decoding (one token per sequence): few CTAs with long key ranges, so the keys are cut until there are about four resident
+        // waves of CTAs (two are resident per SM): the machine is covered and the last wave's tail stays short.
         // The cut depends on the batch size and the pool only, never on the lengths: a captured step stays valid.
         int splits = 1;
         if (n == b.nseq) {
             const long long span = std::min<long long>(c.window, (long long)e->cfg.max_pages * e->cfg.page_size);
             const int ctas = n * c.kv_heads, resident = 2 * sm_count();
-            splits = resident / ctas;
+            splits = (e->attn_waves * resident + ctas - 1) / ctas;
             if (splits > span / 256) splits = (int)(span / 256);
             if (splits > e->gqa_ws_rows / (n * c.heads)) splits = e->gqa_ws_rows / (n * c.heads);
             if (splits > 16) splits = 16;
@@ -599,6 +601,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     if (const char* pm = getenv("WF_SEQ_PAIR_MAX")) e->pair_path_max = atoi(pm);
     if (const char* am = getenv("WF_SEQ_ATTN_MMA")) e->attn_mma = atoi(am);
     if (const char* gm = getenv("WF_SEQ_GRAPH_MAX")) e->graph_max = atoi(gm);
+    if (const char* aw = getenv("WF_SEQ_ATTN_WAVES")) e->attn_waves = atoi(aw) > 0 ? atoi(aw) : 1;
     if (const char* fi = getenv("WF_SEQ_FUSE_INPUT")) e->fuse_input = atoi(fi);
     const wf_seq_config& c = e->cfg;
     const int W = c.width, T = c.max_step_tokens, taps = c.canon_taps;
@@ -766,7 +769,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     e->attn_ws_rows = 4 * 148;
     if (e->dt == WF_BF16 && max_hr > 1) TRY(dalloc_bytes(e, (void**)&e->attn_ws, (size_t)e->attn_ws_rows * (max_hr + 2 * max_H) * sizeof(float)));
     TRY(dalloc_n(e, &e->gate, (size_t)T * max_H));
-    if (e->dt == WF_BF16 && max_gqa_dv) { e->gqa_ws_rows = 8192; TRY(dalloc_bytes(e, (void**)&e->gqa_ws, gqa_attn_mma_workspace(e->gqa_ws_rows, 1, (int)max_gqa_dv))); }
+    if (e->dt == WF_BF16 && max_gqa_dv) { e->gqa_ws_rows = 32768; TRY(dalloc_bytes(e, (void**)&e->gqa_ws, gqa_attn_mma_workspace(e->gqa_ws_rows, 1, (int)max_gqa_dv))); }
     if (max_uff) { TRY(dalloc_n(e, &e->ugu, (size_t)T * 2 * max_uff)); TRY(dalloc_t(e, &e->uhmid, (size_t)T * max_uff)); TRY(dalloc_n(e, &e->uy, (size_t)T * W)); }
     TRY(dalloc_n(e, &e->qkvc, (size_t)T * max_C)); TRY(dalloc_n(e, &e->beta, (size_t)T * max_H)); TRY(dalloc_n(e, &e->decay, (size_t)T * max_H));
     TRY(dalloc_n(e, &e->od, (size_t)T * max_hv));
