@@ -20,11 +20,11 @@ def attn(heads=4, kv_heads=2, dim=16, vdim=16, scale=0.25, kv_from=None):
     return {"type": "attention", "mixer": m, "mlp": None}
 
 
-def dense(ff=40, limit=2.0):
+def dense(ff=40, limit=1.75):
     return {"kind": "dense", "ff": ff, "limit": limit}
 
 
-def moe(experts=8, top=3, count=4, keep=2, ff=20, limit=1.0, scale=1.5, shared=(12, 2.0)):
+def moe(experts=8, top=3, count=4, keep=2, ff=20, limit=1.25, scale=1.75, shared=(12, 2.5)):
     f = {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top, "scale": scale}}
     if count:
         f["router"]["groups"] = {"count": count, "keep": keep}
@@ -37,19 +37,19 @@ def with_ff(layer, ff):
     return dict(layer, mlp=ff)
 
 
-def config(layers, width=48, vocab=70, eps=1e-5, mult=0.4):
+def config(layers, width=48, vocab=70, eps=2e-5, mult=0.4):
     return {"architecture": "Tutizen", "vocab": vocab, "width": width, "norm": {"eps": eps}, "residual_mult": mult, "layers": layers}
 
 
-CFG_MIXED = config([with_ff(attn(), dense()), with_ff(attn(kv_from=0), moe()), with_ff(attn(heads=6, kv_heads=3, dim=8, vdim=12, scale=0.5), moe(experts=6, top=2, count=3, keep=2, ff=16)),
+CFG_MIXED = config([with_ff(attn(), dense()), with_ff(attn(kv_from=0), moe()), with_ff(attn(heads=6, kv_heads=3, dim=8, vdim=12, scale=0.5), moe(experts=6, top=2, count=2, keep=1, ff=16)),
                     attn(heads=6, kv_heads=3, dim=8, vdim=12, scale=0.3, kv_from=2)])
 # equal head counts, one key/value head, one group, top 1, no shared expert, two layers reading the same earlier cache
 CFG_ODD = config([with_ff(attn(heads=3, kv_heads=3, dim=12, vdim=20, scale=0.2), moe(experts=5, top=1, count=1, keep=1, ff=10, shared=None)),
                   with_ff(attn(heads=3, kv_heads=3, dim=12, vdim=20, scale=0.4, kv_from=0), dense(ff=24, limit=0.7)),
                   with_ff(attn(heads=3, kv_heads=3, dim=12, vdim=20, scale=0.1, kv_from=0), moe(experts=4, top=4, count=0, ff=8, scale=0.7)),
                   with_ff(attn(heads=5, kv_heads=1, dim=24, vdim=8, scale=0.15), dense(ff=56, limit=3.0))], width=40, vocab=33, eps=1e-3, mult=1.0)
-CFG_WIDE = config([with_ff(attn(heads=8, kv_heads=2, dim=64, vdim=32, scale=0.125), moe(experts=16, top=4, count=4, keep=3, ff=48, shared=(64, 1.5))),
-                   with_ff(attn(heads=8, kv_heads=2, dim=64, vdim=32, scale=0.125, kv_from=0), dense(ff=192))], width=128, vocab=150, mult=0.25)
+CFG_WIDE = config([with_ff(attn(heads=8, kv_heads=2, dim=64, vdim=32, scale=0.1), moe(experts=16, top=4, count=4, keep=3, ff=48, shared=(64, 1.5))),
+                   with_ff(attn(heads=8, kv_heads=2, dim=64, vdim=32, scale=0.1, kv_from=0), dense(ff=192))], width=128, vocab=150, mult=0.25)
 # nothing here is a multiple of 8: rows of every matrix start unaligned, so the vector / TMA forms of the products must step aside
 CFG_THIN = config([with_ff(attn(heads=3, kv_heads=1, dim=10, vdim=14, scale=0.3), moe(experts=6, top=2, count=3, keep=1, ff=13, shared=(9, 1.0))),
                    with_ff(attn(heads=2, kv_heads=2, dim=6, vdim=10, scale=0.5), dense(ff=21))], width=36, vocab=31)
@@ -137,7 +137,7 @@ def test_position_vectors_and_output_norm(dtype):
         taps.append(m.engine.step_with_layer_tap([s], [len(toks[a:a + 500])], toks[a:a + 500])[1][0])
     got = np.concatenate(taps)
     b = torch.from_numpy(w["l0.mix.o.b"]).double()
-    want = torch.from_numpy(w["embed"]).double()[toks] + O.position_vectors(torch.arange(n), 24) + 0.7 * O.scalar_rms_norm(b, float(w["l0.norm1"]), 1e-5)
+    want = torch.from_numpy(w["embed"]).double()[toks] + O.position_vectors(torch.arange(n), 24) + 0.7 * O.scalar_rms_norm(b, float(w["l0.norm1"]), 2e-5)
     assert np.abs(got - want.numpy()).max() < 2e-5
     # the position vector itself: even entries sines, odd entries cosines of the same angle
     pv = O.position_vectors(torch.tensor([0, 1, 2000]), 24).numpy()
@@ -185,12 +185,12 @@ def test_attention_parts_matter():
     w = t64(make_weights(cfg, 11))
     mx, P = cfg["layers"][0]["mixer"], O.sub(w, "l0.mix.")
     x = torch.from_numpy(_rows(23, 48, 5)).double()
-    base = O.attention(x, P, mx, 1e-5)[0]
-    assert (O.attention(x, dict(P, g=P["g"] * 0), mx, 1e-5)[0] - base).abs().max() > 1e-2
-    assert (O.attention(x, P, dict(mx, scale=mx["scale"] * 1.1), 1e-5)[0] - base).abs().max() > 1e-3
+    base = O.attention(x, P, mx, 2e-5)[0]
+    assert (O.attention(x, dict(P, g=P["g"] * 0), mx, 2e-5)[0] - base).abs().max() > 1e-2
+    assert (O.attention(x, P, dict(mx, scale=mx["scale"] * 1.1), 2e-5)[0] - base).abs().max() > 1e-3
     assert (O.attention(x, P, mx, 1e-1)[0] - base).abs().max() > 1e-3
     swapped = dict(P, q=P["q"].reshape(4, 16, 48)[[0, 2, 1, 3]].reshape(64, 48))     # heads 1 and 2 use different key/value heads
-    assert (O.attention(x, swapped, mx, 1e-5)[0] - base).abs().max() > 1e-2
+    assert (O.attention(x, swapped, mx, 2e-5)[0] - base).abs().max() > 1e-2
     assert abs(float(O.head_slopes(4)[0]) - 0.25) < 1e-12 and abs(float(O.head_slopes(4)[3]) - 2.0 ** -8) < 1e-12
 
 
@@ -364,10 +364,10 @@ def test_far_key_among_hundreds(dtype, far):
     x[far, :16] = u
     x[n - 1, :16] = u
     P, mx = t64(O.sub(w, "l0.mix.")), cfg["layers"][0]["mixer"]
-    want = O.attention(torch.from_numpy(x).double(), P, mx, 1e-5)[0].numpy()
+    want = O.attention(torch.from_numpy(x).double(), P, mx, 2e-5)[0].numpy()
     blind = x.copy()
     blind[far, :16] = 0
-    assert rel_err(O.attention(torch.from_numpy(blind).double(), P, mx, 1e-5)[0].numpy()[-1:], want[-1:])[0] > 0.1
+    assert rel_err(O.attention(torch.from_numpy(blind).double(), P, mx, 2e-5)[0].numpy()[-1:], want[-1:])[0] > 0.1
     m = build(cfg, w, dtype, max_tokens=512, slots=2, page_size=64, max_step_tokens=256)
     s = m.admit()
     got, a = [], 0
@@ -391,7 +391,7 @@ def test_attention_on_tensor_cores_prompts_decoding_and_key_splits(heads, kv_hea
     P, mx = t64(O.sub(w, "l0.mix.")), cfg["layers"][0]["mixer"]
     lens = (333, 70, 129)
     xs = [_rows(n + 4, 64, 122 + n) for n in lens]
-    want = [O.attention(torch.from_numpy(x).double(), P, mx, 1e-5)[0].numpy() for x in xs]
+    want = [O.attention(torch.from_numpy(x).double(), P, mx, 2e-5)[0].numpy() for x in xs]
     m = build(cfg, w, "bfloat16", max_tokens=4096, slots=4, page_size=16, max_step_tokens=512)
     slots = [m.admit() for _ in lens]
     got = [[] for _ in lens]

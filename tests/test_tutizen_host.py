@@ -12,7 +12,7 @@ def _cfg():
         {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 8, "vdim": 12, "scale": 0.3}, "mlp": {"kind": "dense", "ff": 40, "limit": 1.5}},
         {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 8, "vdim": 12, "scale": 0.2, "kv_from": 0},
          "mlp": {"kind": "moe", "expert": {"ff": 16, "limit": 1.0}, "shared": {"ff": 20, "limit": 2.5},
-                 "router": {"experts": 6, "top": 2, "scale": 1.25, "groups": {"count": 3, "keep": 2}}}},
+                 "router": {"experts": 8, "top": 2, "scale": 1.25, "groups": {"count": 4, "keep": 3}}}},
         {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 16, "vdim": 8, "scale": 0.1}, "mlp": None}]}
 
 
@@ -27,7 +27,7 @@ def test_config_reader_takes_every_size_and_constant_from_the_config():
     assert abs(L[0].scale - 0.3) < 1e-7 and abs(L[1].scale - 0.2) < 1e-7
     assert L[1].kv_from == 0 and L[2].kv_from == -1
     assert (L[0].has_ff, L[0].ff, L[0].ff_act) == (_lib.WF_SEQ_FF_DENSE, 40, _lib.WF_SEQ_ACT_CLAMPED) and abs(L[0].ff_limit - 1.5) < 1e-7
-    assert (L[1].has_ff, L[1].experts, L[1].top, L[1].groups, L[1].keep, L[1].ff, L[1].shared_ff) == (_lib.WF_SEQ_FF_ROUTED, 6, 2, 3, 2, 16, 20)
+    assert (L[1].has_ff, L[1].experts, L[1].top, L[1].groups, L[1].keep, L[1].ff, L[1].shared_ff) == (_lib.WF_SEQ_FF_ROUTED, 8, 2, 4, 3, 16, 20)
     assert abs(L[1].router_scale - 1.25) < 1e-7 and abs(L[1].shared_limit - 2.5) < 1e-7 and (L[1].router_act, L[1].group_top, L[1].router_norm) == (1, 2, 1)
     assert L[2].has_ff == _lib.WF_SEQ_FF_NONE
     nc = _lib.SeqConfig()
