@@ -50,7 +50,7 @@ typedef struct wf_seq_layer {
     int router_act;                /* 0 softmax over the experts, 1 sigmoid of each */
     int group_top;                 /* a group's score = sum of its group_top largest choice scores (<= 1: the largest) */
     int router_norm;               /* 1: the chosen scores are divided by their sum (+ 1e-20) */
-    float router_scale;            /* the weights are multiplied by this */
+    float router_scale;            /* the weights are multiplied by this (0 is read as 1) */
     int shared_ff;                 /* > 0: a shared expert of this size runs for every token, times sigmoid(w_sg x) */
     float shared_limit;
 } wf_seq_layer;

@@ -3,7 +3,8 @@
 // A CTA of four warps owns one key/value head and a tile of query rows; a row is a (token, query head of that key/value head's group)
 // pair, so one staged key / value tile serves every head of the group.  Keys and values are staged 64 at a time from the paged cache by
 // cp.async into a ring of two (prompts) or three (decoding) buffers (rows padded by 16 bytes: conflict-free ldmatrix).  Scores S = Q K^T, then the distance penalty and the
-// causal / window mask, an online softmax in float, and O += P V with the weights entering the product as a TWO-term bf16 split
+// causal / window mask (skipped for tiles that every row of the warp sees whole), an online softmax in float in units of log 2 (scale and
+// slopes carry log2 e, the exponentials are exp2), and O += P V with the weights entering the product as a TWO-term bf16 split
 // (p = hi + lo, both products accumulated in float), so that the value sum sees the float weights to 2^-17 rather than rounded to bf16.
 //
 // Two forms of the same tile loop:
@@ -22,6 +23,7 @@ namespace {
 
 constexpr int AM_THREADS = 128;
 constexpr int AM_KT = 64;                 // keys per staged tile
+constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void am_ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -49,7 +51,7 @@ struct AmParams {
     int tq;                  // tokens per CTA tile
     int splits;              // key splits (decode form)
     int ps_log;              // log2 of the page size when that is a power of two, else -1
-    float* part;             // splits > 1: [n * H][splits][dv + 2] (weighted values unnormalised, max, sum)
+    float* part;             // splits > 1: [n * H][splits][dv + 2] (weighted values unnormalised, max in units of log 2, sum)
 };
 
 // DKP / DVP: per-head key and value sizes rounded up to 64 or 128.  DECODE: the decode form.  NSTAGE: staged tiles (ring depth).
@@ -87,15 +89,19 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
     const int row_base = DECODE ? 0 : warp * 16;
     int r_tok[2], r_head[2], r_pos[2];
     bool r_ok[2];
-    float r_slope[2];
+    float r_slope2[2];                                     // slope of the row's head times log2 e
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
         const int r = row_base + g4 + 8 * k;
         const int tk = r >> ap.rp2_log, hg = r & (ap.rp2 - 1);
         r_ok[k] = tk < ntok && hg < rep;
         r_tok[k] = flat0 + tk; r_head[k] = kvh * rep + hg; r_pos[k] = pos0 + tk;
-        r_slope[k] = D.dist_exp > 0.f ? exp2f(-D.dist_exp * (float)(r_head[k] + 1) / (float)D.H) : 0.f;
+        r_slope2[k] = D.dist_exp > 0.f ? exp2f(-D.dist_exp * (float)(r_head[k] + 1) / (float)D.H) * LOG2E : 0.f;
     }
+    const float scale2 = D.scale * LOG2E;
+    // first and last position among the rows of this warp that exist
+    const int wpos_min = pos0 + (row_base >> ap.rp2_log);
+    const int wpos_max = pos0 + ((row_base + 15) >> ap.rp2_log) < pos_last ? pos0 + ((row_base + 15) >> ap.rp2_log) : pos_last;
     // query fragments (A operand), zero beyond d and for rows that do not exist
     uint32_t qf[NKS][4];
 #pragma unroll
@@ -194,36 +200,56 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
                 am_mma(s[2 * jp + 1], qf[ks], kf[2], kf[3]);
             }
         }
-        // ---- distance penalty, mask, online softmax (rows g4 and g4 + 8 of the warp; a row's 4 lanes share it)
+        // ---- distance penalty, mask, online softmax (rows g4 and g4 + 8 of the warp; a row's 4 lanes share it).  Scores are kept in
+        // units of log 2 (scale and slope carry log2 e), so the exponentials are exp2.  The penalty of element (row, key) is
+        // slope * (pos_row - key) = slope * (pos_row - jt0 - 2 t4) - slope * (column constant): one term per row and tile, one FMA per element.
         const int jt0 = t * AM_KT + kw0;
+        float nb[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) nb[k] = -r_slope2[k] * (float)(r_pos[k] - jt0 - 2 * t4);
         float mx[2] = {-INFINITY, -INFINITY};
+        // a tile every row of the warp sees whole needs no mask: its last key is not after the warp's first position, its first not before the window
+        const bool whole = jt0 + KW - 1 <= wpos_min && jt0 > wpos_max - D.window;
+        if (whole) {
 #pragma unroll
-        for (int j = 0; j < NST; ++j)
+            for (int j = 0; j < NST; ++j)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int k = e >> 1, key = jt0 + j * 8 + 2 * t4 + (e & 1);
-                const int dist = r_pos[k] - key;
-                const bool vis = r_ok[k] && dist >= 0 && dist < D.window;
-                const float v = vis ? s[j][e] * D.scale - r_slope[k] * (float)dist : -INFINITY;
-                s[j][e] = v;
-                mx[k] = fmaxf(mx[k], v);
-            }
+                for (int e = 0; e < 4; ++e) {
+                    const int k = e >> 1;
+                    const float v = fmaf(s[j][e], scale2, fmaf(r_slope2[k], (float)(j * 8 + (e & 1)), nb[k]));
+                    s[j][e] = v;
+                    mx[k] = fmaxf(mx[k], v);
+                }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NST; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int k = e >> 1, key = jt0 + j * 8 + 2 * t4 + (e & 1);
+                    const int dist = r_pos[k] - key;
+                    const bool vis = r_ok[k] && dist >= 0 && dist < D.window;
+                    const float v = vis ? fmaf(s[j][e], scale2, fmaf(r_slope2[k], (float)(j * 8 + (e & 1)), nb[k])) : -INFINITY;
+                    s[j][e] = v;
+                    mx[k] = fmaxf(mx[k], v);
+                }
+        }
         float corr[2];
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 1));
             mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 2));
             const float mn = fmaxf(m_run[k], mx[k]);
-            corr[k] = mn == -INFINITY ? 1.f : expf(m_run[k] - mn);      // nothing seen yet: keep the zeros
+            corr[k] = mn == -INFINITY ? 1.f : exp2f(m_run[k] - mn);     // nothing seen yet: keep the zeros
             m_run[k] = mn;
         }
         float ls[2] = {0.f, 0.f};
+        const float msafe[2] = {m_run[0] == -INFINITY ? 0.f : m_run[0], m_run[1] == -INFINITY ? 0.f : m_run[1]};   // exp2(-inf - 0) = 0
 #pragma unroll
         for (int j = 0; j < NST; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int k = e >> 1;
-                const float p = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - m_run[k]);
+                const float p = exp2f(s[j][e] - msafe[k]);
                 s[j][e] = p;
                 ls[k] += p;
             }
@@ -303,7 +329,7 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
         for (int w = 0; w < 4; ++w) mg = fmaxf(mg, sm_m[w * 16 + r]);
         float sc[4], lg = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) { sc[w] = sm_m[w * 16 + r] == -INFINITY ? 0.f : expf(sm_m[w * 16 + r] - mg); lg += sm_l[w * 16 + r] * sc[w]; }
+        for (int w = 0; w < 4; ++w) { sc[w] = sm_m[w * 16 + r] == -INFINITY ? 0.f : exp2f(sm_m[w * 16 + r] - mg); lg += sm_l[w * 16 + r] * sc[w]; }
         if (ap.splits > 1) {
             float* dst = ap.part + (((size_t)tok * D.H + head) * ap.splits + split) * (D.dv + 2);
             for (int c = lane; c < D.dv; c += 32) {
@@ -325,7 +351,7 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
     }
 }
 
-// one warp per (token, head): merge the key splits' partial results, apply the gate
+// one warp per (token, head): merge the key splits' partial results (maxima in units of log 2), apply the gate
 __global__ void gqa_attn_merge_kernel(int rows, int splits, int dv, const float* __restrict__ part, const float* __restrict__ gate, __nv_bfloat16* __restrict__ out) {
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -333,11 +359,11 @@ __global__ void gqa_attn_merge_kernel(int rows, int splits, int dv, const float*
     float mg = -INFINITY;
     for (int z = 0; z < splits; ++z) mg = fmaxf(mg, p[(size_t)z * (dv + 2) + dv]);
     float lg = 0.f;
-    for (int z = 0; z < splits; ++z) { const float m = p[(size_t)z * (dv + 2) + dv]; lg += m == -INFINITY ? 0.f : p[(size_t)z * (dv + 2) + dv + 1] * expf(m - mg); }
+    for (int z = 0; z < splits; ++z) { const float m = p[(size_t)z * (dv + 2) + dv]; lg += m == -INFINITY ? 0.f : p[(size_t)z * (dv + 2) + dv + 1] * exp2f(m - mg); }
     const float mul = (gate ? gate[row] : 1.f) / lg;
     for (int c = lane; c < dv; c += 32) {
         float v = 0.f;
-        for (int z = 0; z < splits; ++z) { const float m = p[(size_t)z * (dv + 2) + dv]; if (m != -INFINITY) v += p[(size_t)z * (dv + 2) + c] * expf(m - mg); }
+        for (int z = 0; z < splits; ++z) { const float m = p[(size_t)z * (dv + 2) + dv]; if (m != -INFINITY) v += p[(size_t)z * (dv + 2) + c] * exp2f(m - mg); }
         out[(size_t)row * dv + c] = __float2bfloat16_rn(v * mul);
     }
 }

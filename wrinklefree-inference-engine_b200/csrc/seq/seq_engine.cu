@@ -328,7 +328,7 @@ int run_delta(wf_seq_engine* e, LayerState& L, const Batch& b) {
     return rc;
 }
 
-// h_t -> y float [n, W] (the output projection's bias is NOT added here: the caller's norm kernel takes it)
+// h_t -> y float [n, W].  In the post form the output projection's bias is NOT added here: the norm kernel that follows takes it
 int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b) {
     const wf_seq_layer& c = L.c;
     const int W = e->cfg.width, n = b.n, nv = c.heads * c.vdim;
@@ -360,6 +360,7 @@ int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b) {
     } else if ((rc = launch_gqa_attn(e->dt, b, D, e->qn, gate, pc, e->og, s))) return rc;
     mark(e, "attn.attention");
     rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
+    if (!rc && L.ob && e->cfg.block_form != WF_SEQ_BLOCK_POST) rc = launch_add_bias(e->dt, e->y, W, L.ob, n, W, s);
     mark(e, "attn.out_gemm");
     return rc;
 }
@@ -390,7 +391,7 @@ int run_ff(wf_seq_engine* e, LayerState& L, const Batch& b) {
     int rc;
     if (c.has_ff == WF_SEQ_FF_DENSE) return run_unit(e, L, b, e->y);
     RouterDims R{c.experts, c.identity, c.top, c.groups, c.keep};
-    R.act = c.router_act; R.group_top = c.group_top; R.norm = c.router_norm; R.scale = c.router_scale;
+    R.act = c.router_act; R.group_top = c.group_top; R.norm = c.router_norm; R.scale = c.router_scale != 0.f ? c.router_scale : 1.f;   // a zeroed struct means unscaled
     if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.router, W, e->z, 1, N, n, N, W), s))) return rc;     // expert logits [| shared gate logit]
     mark(e, "moe.router");
     const float* sh_y = nullptr;
@@ -928,7 +929,7 @@ extern "C" int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, 
         // round the given rows to the storage type exactly as the input convolution's output would be
         rc = launch_gate_mul(e->dt, e->hn, W, e->hn, W, 2, n, W, e->h_t, W, s);
         if (!rc) rc = part == 2 ? run_mixer(e, L, v.b) : run_ff(e, L, v.b);
-        if (!rc && part == 2 && L.ob) rc = launch_add_bias(e->dt, e->y, W, L.ob, n, W, s);
+        if (!rc && part == 2 && L.ob && post) rc = launch_add_bias(e->dt, e->y, W, L.ob, n, W, s);
     } else { set_error("wf_seq_run_part: unknown part %d", part); return WF_ERR_INVALID; }
     if (rc) return rc;
     if (cuda_check(cudaMemcpyAsync(out_host, result, bytes, cudaMemcpyDeviceToHost, s), "out")) return WF_ERR_CUDA;
