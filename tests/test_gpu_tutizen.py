@@ -260,6 +260,33 @@ def test_router_choice_rules():
         m.close()
 
 
+def test_router_reads_the_unrounded_stream():
+    """bfloat16 engine: two router logits that differ by less than bfloat16 resolves (1 and 1 + 2^-9, the larger at the higher index).  The
+    router multiplies the float stream in float, so the larger one wins; on the rounded input they would tie and the lower index would."""
+    f = moe(experts=8, top=1, count=1, keep=1, ff=8, shared=None)
+    cfg = config([with_ff(attn(heads=1, kv_heads=1, dim=8, vdim=8), f)], width=8, vocab=9)
+    w = make_weights(cfg, 35)
+    w["l0.mlp.router"] = np.eye(8, dtype=np.float32)
+    w["l0.mlp.correction"] = np.zeros(8, np.float32)
+    x = np.zeros((9, 8), np.float32)
+    x[:, 3] = 1.0
+    x[:, 6] = 1.0 + 2.0 ** -9
+    ids, _ = O.route(torch.from_numpy(x).double(), torch.zeros(8, dtype=torch.float64), 1, 1, 1, f["router"]["scale"])
+    assert ids[:, 0].tolist() == [6] * 9
+    want = O.feed_forward(torch.from_numpy(x).double(), t64(O.sub(w, "l0.mlp.")), f).numpy()
+    tipped = x.copy()
+    tipped[:, 3] += 2.0 ** -7                                  # what choosing expert 3 instead would give
+    other = O.feed_forward(torch.from_numpy(tipped).double(), t64(O.sub(w, "l0.mlp.")), f).numpy()
+    assert rel_err(other, want).min() > 0.3
+    m = build(cfg, w, "bfloat16")
+    for n in (1, 9):                                           # few-row product, and the plain FMA product
+        s = m.admit()
+        got = m.engine.run_part(0, 3, [s], [n], x[:n])
+        m.release(s)
+        assert rel_err(got, want[:n]).max() < 3e-2, n
+    m.close()
+
+
 # ---------------------------------------------------------------------------------------------------------------- whole models
 @pytest.mark.parametrize("name", ["mixed", "odd", "wide", "thin"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

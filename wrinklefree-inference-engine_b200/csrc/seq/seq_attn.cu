@@ -14,7 +14,7 @@ namespace seq {
 namespace {
 
 constexpr int GA_WARPS = 4;
-constexpr int GA_MAXD = 8;     // per-head sizes up to 32 * 8
+constexpr int GA_MAXD = 16;    // per-head sizes up to 32 * 16
 
 // One block per token; its warps walk the token's head vectors (H query heads, then G key heads, then G value heads): bias, division by the
 // root mean square, store.  Thread h < H also writes the head gate.

@@ -392,8 +392,16 @@ int run_ff(wf_seq_engine* e, LayerState& L, const Batch& b) {
     if (c.has_ff == WF_SEQ_FF_DENSE) return run_unit(e, L, b, e->y);
     RouterDims R{c.experts, c.identity, c.top, c.groups, c.keep};
     R.act = c.router_act; R.group_top = c.group_top; R.norm = c.router_norm; R.scale = c.router_scale != 0.f ? c.router_scale : 1.f;   // a zeroed struct means unscaled
-    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.router, W, e->z, 1, N, n, N, W), s))) return rc;     // expert logits [| shared gate logit]
-    mark(e, "moe.router");
+    // In the post form the sublayer's input IS the float stream, so the router reads it unrounded and multiplies in float — a router is
+    // a 32-bit quantity, and a score that the rounding of its input moved across a neighbour's would change the chosen experts — and the
+    // product and the choice are one kernel.  The sandwich form's input exists only in the storage type: product, then choice.
+    const bool fused_router = e->cfg.block_form == WF_SEQ_BLOCK_POST && router_fused_usable(R, N, W);
+    if (!fused_router) {
+        GemmArgs g = e->cfg.block_form == WF_SEQ_BLOCK_POST ? lin(e->x, 1, W, L.router, W, e->z, 1, N, n, N, W) : lin(e->h_t, 0, W, L.router, W, e->z, 1, N, n, N, W);
+        if (e->cfg.block_form == WF_SEQ_BLOCK_POST && (n > 8 || W % 8)) g.algo = 1;      // up to 8 aligned rows take the few-row stream, which multiplies in float too
+        if ((rc = launch_gemm(e->dt, g, s))) return rc;     // expert logits [| shared gate logit]
+        mark(e, "moe.router");
+    }
     const float* sh_y = nullptr;
     const float* sh_gate = nullptr;
     if (c.shared_ff > 0) {
@@ -408,7 +416,9 @@ int run_ff(wf_seq_engine* e, LayerState& L, const Batch& b) {
     const bool pair_path = c.experts > 0 && pairs <= e->pair_path_max && gemv_pairs_usable(e->dt, gp) && gemv_pairs_usable(e->dt, gd);
     // per-expert token counts are only needed to sort the pairs (the per-pair path sorts nothing)
     if (c.experts > 0 && !pair_path && cuda_check(cudaMemsetAsync(e->counts, 0, (size_t)c.experts * 4, s), "counts")) return WF_ERR_CUDA;
-    if ((rc = launch_moe_route(e->dt, R, n, e->z, N, L.correction, e->ids, e->wts, pair_path ? nullptr : e->counts, s))) return rc;
+    if (fused_router) rc = launch_router_fused(e->dt, R, n, e->x, W, L.router, N, W, e->z, N, L.correction, e->ids, e->wts, pair_path ? nullptr : e->counts, s);
+    else rc = launch_moe_route(e->dt, R, n, e->z, N, L.correction, e->ids, e->wts, pair_path ? nullptr : e->counts, s);
+    if (rc) return rc;
     mark(e, "moe.router");
     if (pair_path) {
         // few tokens (decoding): one weight-streaming product per (token, expert) pair, no sorting
@@ -926,7 +936,9 @@ extern "C" int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, 
     } else if (part == 2 || part == 3) {
         if (part == 3 && !L.c.has_ff) { set_error("wf_seq_run_part: layer %d has no feed-forward", layer); return WF_ERR_INVALID; }
         if (cuda_check(cudaMemcpyAsync(e->hn, in_host, bytes, cudaMemcpyHostToDevice, s), "in")) return WF_ERR_CUDA;
-        // round the given rows to the storage type exactly as the input convolution's output would be
+        // round the given rows to the storage type exactly as the input convolution's output would be (the post form's sublayers also
+        // read the float rows themselves: they are the stream)
+        if (post && cuda_check(cudaMemcpyAsync(e->x, e->hn, bytes, cudaMemcpyDeviceToDevice, s), "in")) return WF_ERR_CUDA;
         rc = launch_gate_mul(e->dt, e->hn, W, e->hn, W, 2, n, W, e->h_t, W, s);
         if (!rc) rc = part == 2 ? run_mixer(e, L, v.b) : run_ff(e, L, v.b);
         if (!rc && part == 2 && L.ob && post) rc = launch_add_bias(e->dt, e->y, W, L.ob, n, W, s);

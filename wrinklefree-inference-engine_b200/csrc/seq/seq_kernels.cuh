@@ -146,6 +146,11 @@ struct RouterDims {
 // z float [n, E + I] (ldz) -> ids [n, top], wts [n, top]; counts[E] += tokens per real expert (zero on entry; null: not counted)
 int launch_moe_route(int dt, const RouterDims& R, int n, const float* z, int ldz, const void* correction, int32_t* ids, float* wts,
                      int32_t* counts, cudaStream_t s);
+// the router product and the choice in one kernel: z[i, 0..NZ) = w[NZ, W] . x[i, :] with x FLOAT (ldx) and float products, then the choice
+// as launch_moe_route makes it from the first E + I logits.  NZ >= E + I: extra rows (a shared expert's gate) are only multiplied.
+bool router_fused_usable(const RouterDims& R, int NZ, int W);
+int launch_router_fused(int dt, const RouterDims& R, int n, const float* x, int ldx, const void* w, int NZ, int W, float* z, int ldz, const void* correction,
+                        int32_t* ids, float* wts, int32_t* counts, cudaStream_t s);
 // from counts: expert segments padded to GEMM_BM rows.  sorted_rows[P] = token of the row or -1; pair_row[n * top] = row of the pair or -1
 // (identity expert); tile_group[P / GEMM_BM] = expert of the row tile or -1.  P = row bound = round_up(n * top, BM) + E * BM.
 // scratch: 2 * E + 1 ints.

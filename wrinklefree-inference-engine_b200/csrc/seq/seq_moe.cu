@@ -18,17 +18,15 @@ __device__ __forceinline__ void warp_argmax(float& v, int& idx) {   // largest v
     }
 }
 
-// one warp per token.  shared: s[N] scores, ch[N] choice scores, gs[G] group scores
+// The choice of one token by one warp.  zr: the token's logits (global or shared); sm: 2 N + groups floats of shared memory
+// (s[N] scores, ch[N] choice scores, gs[G] group scores).
 template <typename T>
-__global__ void moe_route_kernel(RouterDims R, const float* __restrict__ z, int ldz, const T* __restrict__ correction, int32_t* __restrict__ ids,
-                                 float* __restrict__ wts, int32_t* __restrict__ counts) {
-    extern __shared__ float sm[];
+__device__ void route_token(const RouterDims& R, const float* zr, const T* __restrict__ correction, int32_t* __restrict__ ids, float* __restrict__ wts,
+                            int32_t* __restrict__ counts, float* sm, int i, int lane) {
     const int N = R.E + R.I, gsz = N / R.groups;
     float* sc = sm;
     float* ch = sc + N;
     float* gs = ch + N;
-    const int i = blockIdx.x, lane = threadIdx.x;
-    const float* zr = z + (size_t)i * ldz;
     if (R.act == 1) {
         for (int e = lane; e < N; e += 32) { sc[e] = sigmoid_f(zr[e]); ch[e] = sc[e] + to_f(correction[e]); }
     } else {
@@ -93,6 +91,78 @@ __global__ void moe_route_kernel(RouterDims R, const float* __restrict__ z, int 
         __syncwarp();
         for (int k = lane; k < R.top; k += 32) w[k] *= mul;
     }
+}
+
+// one warp per token
+template <typename T>
+__global__ void moe_route_kernel(RouterDims R, const float* __restrict__ z, int ldz, const T* __restrict__ correction, int32_t* __restrict__ ids,
+                                 float* __restrict__ wts, int32_t* __restrict__ counts) {
+    extern __shared__ float sm[];
+    route_token(R, z + (size_t)blockIdx.x * ldz, correction, ids, wts, counts, sm, blockIdx.x, threadIdx.x);
+}
+
+// Router product and choice in one kernel, one block per `tb` tokens: the tokens' FLOAT rows are staged in shared memory, every warp forms
+// the logits of a few outputs for all of them against the storage-type weight rows with float products (a weight row is loaded once per
+// block; NZ rows: the router's outputs, then optional extra rows such as a shared expert's gate), the logits go to z (float [n, ldz])
+// and warp t makes the choice of token t from the shared copy.
+// RF_TB bounds tb.  Measured at 2048 tokens x 31 rows x 2560: 8 tokens per block 70 us, 1 token per block 75 us (the weight rows come from
+// L2 either way; fewer, longer blocks fill the machine worse), while single decoded tokens pay for the unused accumulators: so 1.
+constexpr int RF_THREADS = 256, RF_TB = 1;
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(RF_THREADS) router_fused_kernel(RouterDims R, int n, int tb, const float* __restrict__ x, int ldx, const T* __restrict__ w, int NZ, int W,
+                                                                  float* __restrict__ z, int ldz, const T* __restrict__ correction, int32_t* __restrict__ ids,
+                                                                  float* __restrict__ wts, int32_t* __restrict__ counts) {
+    extern __shared__ __align__(16) float sm[];
+    const int Wp = (W + 3) / 4 * 4, N = R.E + R.I, per = 2 * N + R.groups;
+    float* xs = sm;                                  // [tb][Wp]
+    float* zl = xs + (size_t)tb * Wp;                // [tb][NZ]
+    float* scratch = zl + (size_t)tb * NZ;           // [tb][per]: route_token's
+    const int i0 = blockIdx.x * tb, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nt = n - i0 < tb ? n - i0 : tb;
+    if (RF_TB == 1) { for (int c = threadIdx.x; c < W; c += RF_THREADS) xs[c] = x[(size_t)i0 * ldx + c]; }
+    else for (int idx = threadIdx.x; idx < nt * W; idx += RF_THREADS) { const int t = idx / W, c = idx - t * W; xs[(size_t)t * Wp + c] = x[(size_t)(i0 + t) * ldx + c]; }
+    __syncthreads();
+    constexpr int VN = 16 / sizeof(T);               // elements per 16-byte load
+    for (int e = warp; e < NZ; e += RF_THREADS / 32) {
+        const T* wr = w + (size_t)e * W;
+        float acc[RF_TB];
+#pragma unroll
+        for (int t = 0; t < RF_TB; ++t) acc[t] = 0.f;
+        if (VEC) {
+            for (int c = lane * VN; c < W; c += 32 * VN) {
+                const uint4 q = *reinterpret_cast<const uint4*>(wr + c);
+                const T* v = reinterpret_cast<const T*>(&q);
+                float wv[VN];
+#pragma unroll
+                for (int k = 0; k < VN; ++k) wv[k] = to_f(v[k]);
+#pragma unroll
+                for (int t = 0; t < RF_TB; ++t) {
+                    if (t < nt) {
+#pragma unroll
+                        for (int k = 0; k < VN; k += 4) {      // 16-byte reads of the staged rows too
+                            const float4 a = *reinterpret_cast<const float4*>(xs + (size_t)t * Wp + c + k);
+                            acc[t] = fmaf(a.x, wv[k], acc[t]); acc[t] = fmaf(a.y, wv[k + 1], acc[t]); acc[t] = fmaf(a.z, wv[k + 2], acc[t]); acc[t] = fmaf(a.w, wv[k + 3], acc[t]);
+                        }
+                    }
+                }
+            }
+        } else {
+            for (int c = lane; c < W; c += 32) {
+                const float wv = to_f(wr[c]);
+#pragma unroll
+                for (int t = 0; t < RF_TB; ++t) if (t < nt) acc[t] = fmaf(xs[(size_t)t * Wp + c], wv, acc[t]);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < RF_TB; ++t) {
+            if (t < nt) {
+                const float v = warp_sum(acc[t]);
+                if (lane == 0) { zl[(size_t)t * NZ + e] = v; z[(size_t)(i0 + t) * ldz + e] = v; }
+            }
+        }
+    }
+    __syncthreads();
+    if (warp < nt) route_token(R, zl + (size_t)warp * NZ, correction, ids, wts, counts, scratch + (size_t)warp * per, i0 + warp, lane);
 }
 
 // single block.  scratch: off[E + 1], cursor[E]
@@ -195,6 +265,38 @@ int launch_moe_route(int dt, const RouterDims& R, int n, const float* z, int ldz
     if (dt == WF_BF16) moe_route_kernel<<<n, 32, smem, s>>>(R, z, ldz, (const __nv_bfloat16*)correction, ids, wts, counts);
     else moe_route_kernel<<<n, 32, smem, s>>>(R, z, ldz, (const float*)correction, ids, wts, counts);
     return launch_check(cudaGetLastError(), "moe_route");
+}
+
+namespace {
+size_t router_fused_smem(const RouterDims& R, int NZ, int W, int tb) { return (size_t)tb * ((size_t)(W + 3) / 4 * 4 + NZ + 2 * (R.E + R.I) + R.groups) * sizeof(float); }
+}
+bool router_fused_usable(const RouterDims& R, int NZ, int W) { return router_fused_smem(R, NZ, W, 1) <= 48 * 1024; }
+
+int launch_router_fused(int dt, const RouterDims& R, int n, const float* x, int ldx, const void* w, int NZ, int W, float* z, int ldz, const void* correction,
+                        int32_t* ids, float* wts, int32_t* counts, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    const int N = R.E + R.I;
+    if (R.groups < 1 || N % R.groups || R.keep < 1 || R.keep > R.groups || R.top < 1 || R.top > N || NZ < N) {
+        set_error("router: %d outputs (%d rows), %d groups (keep %d), top %d", N, NZ, R.groups, R.keep, R.top);
+        return WF_ERR_INVALID;
+    }
+    if (!router_fused_usable(R, NZ, W)) { set_error("router: width %d with %d outputs does not fit in shared memory", W, N); return WF_ERR_UNSUPPORTED; }
+    // tokens per block: as many as fit in 48 KB of shared memory (a weight row is then loaded once for all of them), but no more than
+    // leaves a block for every SM
+    int tb = RF_TB;
+    while (tb > 1 && (router_fused_smem(R, NZ, W, tb) > 48 * 1024 || (n + tb - 1) / tb < sm_count())) tb >>= 1;
+    const size_t smem = router_fused_smem(R, NZ, W, tb);
+    const size_t esz = dt == WF_BF16 ? 2 : 4;
+    const bool vec = (W * esz) % 16 == 0 && (((uintptr_t)w) & 15) == 0;
+    const int blocks = (n + tb - 1) / tb;
+    if (dt == WF_BF16) {
+        if (vec) router_fused_kernel<__nv_bfloat16, true><<<blocks, RF_THREADS, smem, s>>>(R, n, tb, x, ldx, (const __nv_bfloat16*)w, NZ, W, z, ldz, (const __nv_bfloat16*)correction, ids, wts, counts);
+        else router_fused_kernel<__nv_bfloat16, false><<<blocks, RF_THREADS, smem, s>>>(R, n, tb, x, ldx, (const __nv_bfloat16*)w, NZ, W, z, ldz, (const __nv_bfloat16*)correction, ids, wts, counts);
+    } else {
+        if (vec) router_fused_kernel<float, true><<<blocks, RF_THREADS, smem, s>>>(R, n, tb, x, ldx, (const float*)w, NZ, W, z, ldz, (const float*)correction, ids, wts, counts);
+        else router_fused_kernel<float, false><<<blocks, RF_THREADS, smem, s>>>(R, n, tb, x, ldx, (const float*)w, NZ, W, z, ldz, (const float*)correction, ids, wts, counts);
+    }
+    return launch_check(cudaGetLastError(), "router_fused");
 }
 
 int launch_moe_plan(const RouterDims& R, int n, const int32_t* ids, const int32_t* counts, int32_t* scratch, int32_t* sorted_rows,
